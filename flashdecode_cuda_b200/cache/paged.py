@@ -53,7 +53,9 @@ class KVGroupSpec:
     only blocks that reach into the chunk of the next query are kept.
     ``v_head_dim``: size of a value head where it differs from a key head's.
     ``keys_only``: nothing but one vector per position and head is kept; it is read
-    as key and as value (``v_pool`` is ``k_pool``)."""
+    as key and as value (``v_pool`` is ``k_pool``).  ``keep_first``: with a window, the first so many
+    positions of a sequence stay visible to every later query, so the blocks that hold them are never
+    given back."""
     n_layers: int
     n_kv_heads: int
     head_dim: int
@@ -61,6 +63,7 @@ class KVGroupSpec:
     chunk: Optional[int] = None
     v_head_dim: Optional[int] = None
     keys_only: bool = False
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -283,7 +286,8 @@ class PagedCache:
             dead_cols = g.spec.first_needed(rec.length) // self.block_size
             blocks = rec.blocks[gi]
             freed = []
-            for c in range(min(dead_cols, len(blocks))):
+            kept_cols = self.blocks_needed(g.spec.keep_first)      # blocks of the positions that stay visible for good
+            for c in range(kept_cols, min(dead_cols, len(blocks))):
                 if blocks[c] >= 0:
                     freed.append(blocks[c])
                     blocks[c] = -1
@@ -326,7 +330,8 @@ class PagedCache:
         for g in self.groups:
             for s in slots:
                 n = self._record(s).length
-                n -= g.spec.first_needed(max(0, n - 1))      # what the last cached token's query saw
+                first = g.spec.first_needed(max(0, n - 1))   # what the last cached token's query saw
+                n -= max(0, first - g.spec.keep_first)
                 total += n * g.bytes_per_token()
         return total
 

@@ -15,6 +15,7 @@ from ..registry import architecture
 from .lonasun import LonasunConfig
 from .nizazen import NizazenConfig
 from .qwen2 import ConfigError, Qwen2Config
+from .revelix import RevelixConfig
 
 PRESET_DIR = Path(__file__).resolve().parent / "presets"
 
@@ -61,4 +62,4 @@ def load_config(source: Union[str, Path, Dict[str, Any]]):
     raise ConfigError(f"no config.json at {source!r} and no preset of that name; presets: {preset_names()}")
 
 
-__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "NizazenConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]
+__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "NizazenConfig", "RevelixConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]

@@ -30,6 +30,13 @@ struct AttnParams {
     int QT, n_splits, split_len, window;
     int chunk;                 // > 0: a query at position i sees key j <= i only if i / chunk == j / chunk
     float scale;
+    // The CUDA-core kernel only (the launchers of the other kernels are not called when any of these is set):
+    float softcap;             // > 0: score <- softcap * tanh(score / softcap) after scaling
+    int keep_first;            // with a window: keys at positions below this stay visible however far back they lie
+    const float* sink;         // [n_q] or null: exp(sink[h]) is one more term of head h's softmax denominator
+    int v_rep;                 // > 1: every query head's weights are applied to each of v_rep value heads (the pool's
+                               // n_kv heads); out is then [T, n_q, v_rep, dv]
+    int out_f32;               // out is float whatever the type of q and the pools
     // decode steps on the tensor cores only: memory that a later kernel streams (the next part's first weights), or
     // null; every CTA asks L2 for its share once its own keys and values are through
     const unsigned char* pf_ptr;

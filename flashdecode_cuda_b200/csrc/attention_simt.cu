@@ -3,7 +3,12 @@
 // size of their own), any group size up to 64, any block size, an optional
 // sliding window or chunked visibility (keys of the query's own chunk of
 // `chunk` positions only, chunks counted from the start of the sequence),
-// float or bfloat16 storage.  One kernel serves both kinds of step:
+// float or bfloat16 storage.  Options that only this kernel has: scores capped by a
+// tanh, a window that also keeps the first positions of the sequence (the key
+// tiles between those and the window's start are skipped), a learned term per
+// head in the softmax denominator that has no key and no value, and weights that
+// are applied to every value head instead of the query head's own (the caller
+// mixes the heads' outputs afterwards).  One kernel serves both kinds of step:
 //
 //  * prompts: a CTA takes QT consecutive query tokens of one sequence and one
 //    KV head, i.e. R = QT * G query rows that share the same keys, and walks
@@ -61,7 +66,8 @@ template <> __device__ __forceinline__ void load_chunk4<__nv_bfloat16>(const __n
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_tile_kernel(const AttnParams p) {
-    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int b = blockIdx.z;
+    const int kvh = blockIdx.y / p.v_rep, vh = p.v_rep > 1 ? blockIdx.y - kvh * p.v_rep : kvh;     // key head, value head
     const int tile = blockIdx.x / p.n_splits, split = blockIdx.x - tile * p.n_splits;
     const int slot = p.row_slot[b];
     if (slot < 0) return;
@@ -76,10 +82,18 @@ attn_tile_kernel(const AttnParams p) {
     int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
     if (p.chunk > 0) lo = max(lo, (p_first / p.chunk) * p.chunk);   // the earliest chunk start among the tile's queries
     int hi = p_first + nq;                                   // keys 0 .. last query position
+    // kept first positions that lie before the window's start: keys [s_lo, kf) are visited too, the tiles between skipped
+    int kf = (p.window > 0 && p.keep_first > 0) ? min(p.keep_first, lo) : 0;
+    int s_lo = 0;
     if (p.n_splits > 1) {
-        lo = max(lo, split * p.split_len);
+        s_lo = split * p.split_len;
+        lo = max(lo, s_lo);
         hi = min(hi, (split + 1) * p.split_len);
+        kf = min(kf, hi);
     }
+    if (kf <= s_lo) kf = 0;
+    const int t_begin = kf > 0 ? (s_lo / KT) * KT : (lo / KT) * KT;
+    const int kf_end = ((kf + KT - 1) / KT) * KT, lo_tile = (lo / KT) * KT;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int KPAD = Pad<T>::v;
@@ -92,6 +106,7 @@ attn_tile_kernel(const AttnParams p) {
     T* k_s = v_s + KT * dv;                                           // [KT][d + KPAD]
 
     __shared__ int row_s[KT];                    // per token of the tile: its row in the pools, -1 outside [lo, hi)
+    __shared__ int vrow_s[KT];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const T* qg = static_cast<const T*>(p.q);
     const T* kp = static_cast<const T*>(p.k_pool);
@@ -123,7 +138,9 @@ attn_tile_kernel(const AttnParams p) {
     const int cprv = dv / EPC;                    // chunks per value row
     const int bs = p.block_size;
 
-    for (int t0 = (lo / KT) * KT; t0 < hi; t0 += KT) {
+    for (int t0 = t_begin; t0 < hi; t0 += KT) {
+        if (t0 >= kf_end && t0 < lo_tile) t0 = lo_tile;          // nothing visible between the kept keys and the window
+        if (t0 >= hi) break;
         __syncthreads();   // previous tile consumed (and q_s written, first time round)
         // stage keys and values of this tile; tokens outside [lo, hi) read as zero.  The tile's block numbers are looked
         // up once per token, then every thread has several independent 16-byte loads in flight (one lookup and one
@@ -131,12 +148,17 @@ attn_tile_kernel(const AttnParams p) {
         if (tid < KT) {
             const int t = t0 + tid;
             int base = -1;
-            if (t >= lo && t < hi) {
+            int vbase = -1;
+            if ((t >= lo || (t < kf && t >= s_lo)) && t < hi) {
                 const int blk = p.block_table[(size_t)slot * p.max_blocks + t / bs];
                 if (blk < 0 || blk >= p.num_blocks) set_status(p.status, STATUS_BAD_BLOCK);
-                else base = (blk * p.n_kv + kvh) * bs + (t % bs);          // the token's row in either pool
+                else {
+                    base = (blk * p.n_kv + kvh) * bs + (t % bs);          // the token's row in the key pool
+                    vbase = (blk * p.n_kv + vh) * bs + (t % bs);          // and in the value pool
+                }
             }
             row_s[tid] = base;
+            vrow_s[tid] = vbase;
         }
         __syncthreads();
         {
@@ -152,7 +174,7 @@ attn_tile_kernel(const AttnParams p) {
                         const int tt = c / per_tok, cc = c - tt * per_tok;
                         const int base = row_s[tt];
                         if (base >= 0)
-                            x4[u] = cc >= cpr ? *reinterpret_cast<const uint4*>(vp + (size_t)base * dv + (cc - cpr) * EPC)
+                            x4[u] = cc >= cpr ? *reinterpret_cast<const uint4*>(vp + (size_t)vrow_s[tt] * dv + (cc - cpr) * EPC)
                                               : *reinterpret_cast<const uint4*>(kp + (size_t)base * d + cc * EPC);
                     }
                 }
@@ -202,9 +224,12 @@ attn_tile_kernel(const AttnParams p) {
             if (r >= R) break;
             {
                 const int qpos = p_first + r / G;
-                const bool valid = t >= lo && t < hi && t <= qpos && (p.window <= 0 || qpos - t < p.window) &&
+                const bool valid = (t >= lo || (t < kf && t >= s_lo)) && t < hi && t <= qpos &&
+                                   (p.window <= 0 || qpos - t < p.window || t < p.keep_first) &&
                                    (p.chunk <= 0 || t >= (qpos / p.chunk) * p.chunk);
-                const float sv = valid ? s[i] : -INFINITY;
+                float sc = s[i];
+                if (p.softcap > 0.f) sc = p.softcap * tanhf(sc / p.softcap);
+                const float sv = valid ? sc : -INFINITY;
                 const float m_new = fmaxf(m_run[i], warp_max(sv));
                 float pr = 0.f, alpha = 1.f;
                 if (m_new != -INFINITY) {
@@ -262,18 +287,31 @@ attn_tile_kernel(const AttnParams p) {
         const int r = rg + i * RG;
         if (r >= R) continue;
         const int qi = r / G, g = r - qi * G;
-        const size_t row = (size_t)(tok0 + qi) * p.n_q + kvh * G + g;
+        const int head = kvh * G + g;
+        size_t row = (size_t)(tok0 + qi) * p.n_q + head;
+        if (p.v_rep > 1) row = row * p.v_rep + vh;
         if (p.n_splits > 1) {
             const size_t pi = row * p.n_splits + split;
             if (dc == 0) { p.part_m[pi] = alpha_s[r]; p.part_l[pi] = l_s[r]; }
             *reinterpret_cast<float4*>(p.part_acc + pi * dv + dc * 4) =
                 make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
         } else {
-            const float l = l_s[r];
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            T* o = og + row * dv + dc * 4;
+            float l = l_s[r], f = 1.f;
+            if (p.sink != nullptr) {                 // one more term in the denominator: exp(sink), no key, no value
+                const float sk = p.sink[head], m = alpha_s[r];
+                const float m2 = fmaxf(m, sk);
+                f = m == -INFINITY ? 0.f : expf(m - m2);
+                l = l * f + expf(sk - m2);
+            }
+            const float inv = l > 0.f ? f / l : 0.f;
+            if (p.out_f32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(p.out) + row * dv + dc * 4) =
+                    make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+            } else {
+                T* o = og + row * dv + dc * 4;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] = from_float<T>(acc[i][j] * inv);
+                for (int j = 0; j < 4; ++j) o[j] = from_float<T>(acc[i][j] * inv);
+            }
         }
     }
 }
@@ -289,7 +327,8 @@ template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                     const float* __restrict__ part_acc, T* __restrict__ out,
                                     const int* __restrict__ tok_row, const int* __restrict__ row_slot,
-                                    int n_q, int d, int n_splits) {
+                                    int n_q, int d, int n_splits, const float* __restrict__ sink, int v_rep,
+                                    int out_f32) {
     __shared__ float w_s[COMBINE_MAX_SPLITS];
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -297,8 +336,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
     const int tok = blockIdx.y, h = blockIdx.x;
     const size_t row = (size_t)tok * n_q + h;
     T* o = out + row * d;
+    float* of = reinterpret_cast<float*>(out) + row * d;       // the same row when the output is float whatever T is
     if (row_slot[tok_row[tok]] < 0) {
-        for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_float<T>(0.f);
+        for (int j = threadIdx.x; j < d; j += blockDim.x) { if (out_f32) of[j] = 0.f; else o[j] = from_float<T>(0.f); }
         return;
     }
     const float* pm = part_m + row * n_splits;
@@ -313,6 +353,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
     __syncthreads();
     m = -INFINITY;
     for (int w = 0; w < nwarps; ++w) m = fmaxf(m, red[w]);
+    const float sk = sink != nullptr ? sink[h / v_rep] : -INFINITY;     // the denominator's keyless term
+    m = fmaxf(m, sk);
     __syncthreads();
     // weights and their sum, in split order within a thread; the block sum order is fixed too
     float lsum = 0.f;
@@ -322,7 +364,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
         w_s[s] = w;
         lsum += ls * w;
     }
-    const float l = block_sum(lsum, red);
+    float l = block_sum(lsum, red);
+    if (sink != nullptr) l += expf(sk - m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const float* pa = part_acc + row * n_splits * d;
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
@@ -335,7 +378,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
             a = fmaf(a2, w_s[s + 2], a); a = fmaf(a3, w_s[s + 3], a);
         }
         for (; s < n_splits; ++s) a = fmaf(pa[(size_t)s * d + j], w_s[s], a);
-        o[j] = from_float<T>(a * inv);
+        if (out_f32) of[j] = a * inv; else o[j] = from_float<T>(a * inv);
     }
 }
 
@@ -356,7 +399,7 @@ static int launch_attn(const AttnParams& p, int n_rows, int max_q_len, cudaStrea
         configured = smem;
     }
     const int q_tiles = (max_q_len + p.QT - 1) / p.QT;
-    dim3 grid(q_tiles * p.n_splits, p.n_kv, n_rows);
+    dim3 grid(q_tiles * p.n_splits, p.n_kv * p.v_rep, n_rows);
     k<<<grid, ATT_THREADS, smem, stream>>>(p);
     return check_launch("attention");
 }
@@ -396,8 +439,14 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                           const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                           int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                           int n_splits, int split_len, float* scratch, int* counters, int* status, int use_mma,
-                          cudaStream_t stream, const void* prefetch = nullptr, unsigned long long prefetch_bytes = 0) {
+                          cudaStream_t stream, const void* prefetch = nullptr, unsigned long long prefetch_bytes = 0,
+                          float softcap = 0.f, int keep_first = 0, const float* sink = nullptr, int v_rep = 1,
+                          int out_f32 = 0) {
     if (n_rows == 0 || T == 0) return 0;
+    FD_REQUIRE(softcap >= 0.f && keep_first >= 0 && v_rep >= 1 && (v_rep == 1 || v_rep == n_kv), -2,
+               "attention: soft cap %g, %d kept first keys, weights applied to %d value heads of %d", softcap, keep_first,
+               v_rep, n_kv);
+    if (softcap > 0.f || (keep_first > 0 && window > 0) || sink != nullptr || v_rep > 1 || out_f32) use_mma = 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
     FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= D_MAX, -2, "attention: head size %d must be a multiple of 8 in [8, %d]", d, D_MAX);
@@ -419,7 +468,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     AttnParams p;
     p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.out = out;
-    const size_t n_part = (size_t)T * n_q * n_splits;
+    const size_t n_part = (size_t)T * n_q * v_rep * n_splits;
     // accumulators first: they are stored as float4 and must stay 16-byte aligned
     p.part_acc = scratch;
     p.part_m = scratch ? scratch + n_part * dv : nullptr;
@@ -430,6 +479,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;
     p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d; p.dv = dv; p.chunk = chunk;
     p.n_kv_pool = n_kv; p.kv_div = 1;
+    p.softcap = softcap; p.keep_first = keep_first; p.sink = sink; p.v_rep = v_rep; p.out_f32 = out_f32;
     if (dv != d) use_mma = 0;          // the tensor-core kernels keep keys and values of one size
     int qt = fd_attn_simt_qt(G);
     if ((d > 256 || dv > 256) && qt > RWIDE / G) qt = RWIDE / G;
@@ -453,14 +503,29 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);
     if (rc != 0 || n_splits == 1) return rc;
-    dim3 grid(n_q, T);
+    dim3 grid(n_q * v_rep, T);
     if (dtype == 0)
         return launch("attention_combine", attn_combine_kernel<float>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
                       (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (float*)out, tok_row,
-                      row_slot, n_q, dv, n_splits);
+                      row_slot, n_q * v_rep, dv, n_splits, sink, v_rep, out_f32);
     return launch("attention_combine", attn_combine_kernel<bf16>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
                   (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (bf16*)out, tok_row,
-                  row_slot, n_q, dv, n_splits);
+                  row_slot, n_q * v_rep, dv, n_splits, sink, v_rep, out_f32);
+}
+
+// out[t, h, :] = scale * sum_g mix[h, g] * o[t, g, vh(h), :] with vh(h) = h / (n_q / n_kv): every head takes the other
+// heads' weights on the values of its own key/value head.  o [T, n_q, n_kv, dv] float; out rows of ld_out elements.
+template <typename T>
+__global__ void attn_head_mix_kernel(const float* __restrict__ o, const float* __restrict__ mix, T* __restrict__ out,
+                                     int ld_out, int n_q, int n_kv, int dv, float scale) {
+    const int t = blockIdx.y, h = blockIdx.x;
+    const int vh = h / (n_q / n_kv);
+    const float* ot = o + (size_t)t * n_q * n_kv * dv;
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+        float a = 0.f;
+        for (int g = 0; g < n_q; ++g) a = fmaf(mix[h * n_q + g], ot[((size_t)g * n_kv + vh) * dv + j], a);
+        out[(size_t)t * ld_out + h * dv + j] = from_float<T>(a * scale);
+    }
 }
 
 // The CUDA-core kernel for every case.
@@ -507,4 +572,36 @@ extern "C" int fd_attention_mma_sync(const void* q, const void* k_pool, const vo
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
                           window, dv, chunk, n_splits, split_len, scratch, counters, status, 2, stream);
+}
+
+// The CUDA-core kernel with its own options: softcap > 0 caps the scaled scores by a tanh; keep_first: with a window, the
+// first so many positions stay visible; sink [n_q] (or null): a keyless term exp(sink[h]) in head h's denominator;
+// v_rep == n_kv: every query head's weights are applied to all value heads and out is [T, n_q, n_kv, dv] (scratch for
+// the split form: fd_attn_scratch_floats(T, n_q * n_kv, dv, n_splits)); out_f32: out is float.
+extern "C" int fd_attention_ext(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                                const int* block_table, int max_blocks, int num_blocks, int block_size,
+                                const int* tok_row, const int* row_slot, const int* row_q_start,
+                                const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
+                                int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
+                                int n_splits, int split_len, float* scratch, int* status, float softcap, int keep_first,
+                                const float* sink, int v_rep, int out_f32, cudaStream_t stream) {
+    return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
+                          row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
+                          window, dv, chunk, n_splits, split_len, scratch, nullptr, status, 0, stream, nullptr, 0,
+                          softcap, keep_first, sink, v_rep, out_f32);
+}
+
+// o [T, n_q, n_kv, dv] float, mix [n_q, n_q] float; out (dtype 0 float32, 1 bfloat16): pointer to the first output
+// column, rows of ld_out elements.
+extern "C" int fd_attn_head_mix(const float* o, const float* mix, void* out, int ld_out, int dtype, int T, int n_q,
+                                int n_kv, int dv, float scale, cudaStream_t stream) {
+    if (T == 0) return 0;
+    FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0 && T <= 65535, -2, "attn_head_mix: %d heads on %d, %d tokens", n_q, n_kv, T);
+    const dim3 grid(n_q, T);
+    const int threads = dv >= 128 ? 128 : (dv + 31) / 32 * 32;
+    if (dtype == 0)
+        return launch("attn_head_mix", attn_head_mix_kernel<float>, grid, dim3(threads), 0, stream, dim3(1, 1, 1), o, mix,
+                      (float*)out, ld_out, n_q, n_kv, dv, scale);
+    return launch("attn_head_mix", attn_head_mix_kernel<bf16>, grid, dim3(threads), 0, stream, dim3(1, 1, 1), o, mix,
+                  (bf16*)out, ld_out, n_q, n_kv, dv, scale);
 }

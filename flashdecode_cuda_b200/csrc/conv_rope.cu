@@ -5,8 +5,9 @@
 //    and v channel over the token's last `taps` projected values (those of
 //    earlier steps come from the sequence's state, zeros before its start), the
 //    rotation of the first `rot` dimensions of every q and k head (dimension i
-//    paired with i + rot/2) at the token's position, q to its buffer and k, v to
-//    the paged cache (value heads may have a size of their own);
+//    paired with i + rot/2, or, `interleaved`, dimension 2i with 2i + 1) at the
+//    token's position, q to its buffer and k, v to the paged cache (value heads
+//    may have a size of their own);
 //  * conv_state_update: the sequence's state becomes the last taps - 1 projected
 //    values after the step;
 //  * gate_mul: out = a * sigmoid(g), g read with a row stride (the gate columns
@@ -56,7 +57,7 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
                         T* __restrict__ k_pool, T* __restrict__ v_pool,
                         const int* __restrict__ block_table, int max_blocks, int num_blocks,
                         int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
-                        int update_state, int* status, int n_tok, int tpc) {
+                        int update_state, int* status, int n_tok, int tpc, int interleaved) {
     extern __shared__ float y_s[];                 // [tpc][width]: the head's convolved channels of every token
     __shared__ int m_slot[CONV_TPC], m_start[CONV_TPC], m_i[CONV_TPC], m_pos[CONV_TPC], m_move[CONV_TPC];
     __shared__ long long m_dst[CONV_TPC];          // element offset of the token's key or value row of this head, or -1
@@ -173,12 +174,18 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
         if (!is_v && j < rot && pos >= 0 && pos < table_len) {      // q and k heads: rotate the leading `rot` dimensions
             const float* cs = cos_t + (size_t)pos * half;
             const float* sn = sin_t + (size_t)pos * half;
+            if (interleaved) {                     // the pair is this thread's own two channels
+                const float c = cs[j >> 1], sv = sn[j >> 1];
+                v[0] = y0[tt] * c - y1[tt] * sv;
+                v[1] = y1[tt] * c + y0[tt] * sv;
+            } else {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int je = j + e;
-                if (je >= rot) continue;
-                if (je < half) v[e] = v[e] * cs[je] - y_s[tt * width + je + half] * sn[je];
-                else v[e] = v[e] * cs[je - half] + y_s[tt * width + je - half] * sn[je - half];
+                for (int e = 0; e < 2; ++e) {
+                    const int je = j + e;
+                    if (je >= rot) continue;
+                    if (je < half) v[e] = v[e] * cs[je] - y_s[tt * width + je + half] * sn[je];
+                    else v[e] = v[e] * cs[je - half] + y_s[tt * width + je - half] * sn[je - half];
+                }
             }
         }
         if (is_q) {
@@ -267,7 +274,7 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
                                    const int* row_q_start, const int* row_q_len, void* k_pool, void* v_pool,
                                    const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
                                    int n_q, int n_kv, int d, int dv, int taps, int write_kv, int update_state,
-                                   int* status, cudaStream_t stream) {
+                                   int* status, int interleaved, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(n_q > 0 && n_kv > 0 && d > 0 && dv > 0 && taps >= 1 && block_size > 0, -2, "conv_rope_append: bad sizes");
     FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, -2, "conv_rope_append: %d rotated dimensions of a head of %d", rot, d);
@@ -288,13 +295,13 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
         return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
                       conv_w, state, (float*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                       row_q_len, (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q,
-                      n_kv, d, dv, taps, write_kv, update_state, status, T, tpc);
+                      n_kv, d, dv, taps, write_kv, update_state, status, T, tpc, interleaved);
     }
     auto k = conv_rope_append_kernel<bf16>;
     return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
                   conv_w, state, (bf16*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                   row_q_len, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv,
-                  d, dv, taps, write_kv, update_state, status, T, tpc);
+                  d, dv, taps, write_kv, update_state, status, T, tpc, interleaved);
 }
 
 extern "C" int fd_conv_state_update(const void* proj, int ld, int dtype, float* state, const int* row_slot,

@@ -167,6 +167,11 @@ class Model:
         params = dict(spec.params)
         if isinstance(params.get("position"), str):
             params["position"] = self.positions[params["position"]]
+        for k, v in params.items():          # parts made of parts (mixers side by side): built first, handed over whole
+            if isinstance(v, PartSpec):
+                params[k] = self._build(v)
+            elif isinstance(v, (list, tuple)) and v and all(isinstance(e, PartSpec) for e in v):
+                params[k] = [self._build(e) for e in v]
         if spec.kind == "position":
             return cls(**params)
         return cls(prefix=spec.prefix, **params)

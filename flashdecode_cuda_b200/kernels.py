@@ -96,7 +96,15 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P],
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
-        "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
+        "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, P],
+        "fd_attn_head_mix": [P, P, P, I, I, I, I, I, I, F, P],
+        "fd_add_dyn_tanh": [P, I, P, I, P, P, F, P, I, P, I, I, P],
+        "fd_quad_exp_act": [P, P, I, P, LL, P],
+        "fd_scale_f32": [P, LL, F, P],
+        "fd_axpy_f32": [P, P, I, LL, F, I, P],
+        "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, P],
+        "fd_head_norm_gate": [P, P, P, I, P, I, I, I, I, I, F, F, P],
         "fd_conv_state_update": [P, I, I, P, P, P, P, I, I, I, P],
         "fd_gate_mul": [P, P, I, P, I, I, I, P],
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
@@ -676,6 +684,139 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                split_len, scratch, status, chunk=chunk)
 
 
+def attention_ext(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                  block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
+                  row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
+                  n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                  window: int = 0, n_splits: int = 1, split_len: int = 0,
+                  scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, chunk: int = 0,
+                  softcap: float = 0.0, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
+                  all_value_heads: bool = False) -> None:
+    """Attention on the CUDA cores with the options only that kernel has.  ``softcap`` > 0: the scaled scores
+    become softcap * tanh(score / softcap).  ``keep_first``: with a window, keys at positions below it stay
+    visible.  ``sink`` [n_q] float32: exp(sink[h]) is one more term of head h's softmax denominator; it has
+    no key and no value.  ``all_value_heads``: every query head's weights are applied to each of the ``n_kv``
+    value heads; ``out`` is then float32 [T, n_q, n_kv, dv] (for ``attn_head_mix``).  Otherwise ``out`` is
+    [T, n_q * dv] in q's dtype, or float32 if it is given so."""
+    T = q.shape[0]
+    num_blocks, _, block_size, _ = k_pool.shape
+    v_dim = v_pool.shape[-1]
+    v_rep = n_kv if all_value_heads else 1
+    assert q.dtype == k_pool.dtype == v_pool.dtype and k_pool.shape[-1] == head_dim
+    assert out.dtype in (q.dtype, torch.float32) and out.numel() == T * n_q * v_rep * v_dim
+    assert not all_value_heads or out.dtype == torch.float32
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_q)
+    if n_splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32
+        assert scratch.numel() >= attention_scratch_floats(T, n_q * v_rep, v_dim, n_splits)
+    _check(lib().fd_attention_ext(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype), _ptr(block_table), block_table.shape[1],
+        num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
+        n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), int(v_dim), int(chunk), n_splits,
+        split_len, _ptr(scratch), _ptr(status), float(softcap), int(keep_first), _ptr(sink), v_rep,
+        int(out.dtype == torch.float32 and q.dtype != torch.float32 or all_value_heads), _stream()))
+
+
+def _col_ptr(t: torch.Tensor, first_col: int) -> int:
+    assert t.is_contiguous() and t.dim() == 2 and 0 <= first_col < t.shape[1]
+    return _ptr(t) + first_col * t.element_size()
+
+
+def attn_head_mix(o: torch.Tensor, mix: torch.Tensor, out: torch.Tensor, first_col: int, n_q: int, n_kv: int,
+                  v_head_dim: int, scale: float = 1.0) -> None:
+    """out[t, first_col + h dv + j] = scale * sum_g mix[h, g] o[t, g, h // (n_q / n_kv), j]: the heads' attention
+    weights mixed after the softmax, each head on the values of its own key/value head.  ``o`` float32
+    [T, n_q, n_kv, dv] from ``attention_ext(all_value_heads=True)``; ``mix`` float32 [n_q, n_q]; ``out`` [T, ld]."""
+    T, dv = o.shape[0], v_head_dim
+    assert o.dtype == torch.float32 and o.numel() == T * n_q * n_kv * dv and mix.dtype == torch.float32
+    assert mix.shape == (n_q, n_q) and out.shape[0] == T and first_col + n_q * dv <= out.shape[1]
+    _check(lib().fd_attn_head_mix(_ptr(o), _ptr(mix), _col_ptr(out, first_col), out.shape[1], _dt(out.dtype), T, n_q,
+                                  n_kv, dv, float(scale), _stream()))
+
+
+def add_dyn_tanh(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                 alpha: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,
+                 write_resid: bool = True) -> None:
+    """resid[r] += delta[r]; out[j] = tanh(alpha * resid[r]) * weight + bias with r = rows[j] (or j).  No mean, no
+    variance.  ``resid``, ``weight`` and ``bias`` float32; ``delta`` [*, H] float32 or bfloat16, or None."""
+    H = resid.shape[-1]
+    if n_out is None:
+        n_out = rows.numel() if rows is not None else resid.numel() // H
+    assert resid.dtype == weight.dtype == bias.dtype == torch.float32 and weight.numel() == bias.numel() == H
+    assert out.shape[-1] == H and (delta is None or (delta.dim() == 2 and delta.shape[-1] == H))
+    _check(lib().fd_add_dyn_tanh(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid), int(write_resid),
+                                 _ptr(weight), _ptr(bias), float(alpha), _ptr(out), _dt(out.dtype), _ptr(rows), n_out, H,
+                                 _stream()))
+
+
+def quad_exp_act(x: torch.Tensor, pq: torch.Tensor, out: torch.Tensor) -> None:
+    """out = softplus(p) z^2 + z / 2 where z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 elsewhere; ``pq`` float32
+    [2] = (p, q) on the device.  Float arithmetic, one rounding."""
+    assert x.shape == out.shape and x.dtype == out.dtype and pq.dtype == torch.float32 and pq.numel() == 2
+    _check(lib().fd_quad_exp_act(_ptr(x), _ptr(out), _dt(x.dtype), _ptr(pq), x.numel(), _stream()))
+
+
+def scale_(x: torch.Tensor, s: float) -> None:
+    """x <- x * s in place; x float32."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().fd_scale_f32(_ptr(x), x.numel(), float(s), _stream()))
+
+
+def axpy_f32(y: torch.Tensor, x: torch.Tensor, s: float, accumulate: bool = True) -> None:
+    """y <- s * x (+ y if ``accumulate``); y float32, x float32 or bfloat16 of the same shape."""
+    assert y.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous()
+    _check(lib().fd_axpy_f32(_ptr(y), _ptr(x), _dt(x.dtype), y.numel(), float(s), int(accumulate), _stream()))
+
+
+SCAN_DECAY, SCAN_GATED = 0, 1
+
+
+def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: torch.Tensor, out: torch.Tensor,
+                mode: int, row_slot: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
+                row_ctx_len: torch.Tensor, n_rows: int, n_heads: int, head_dim: int, v_head_dim: int,
+                write_state: bool, status: torch.Tensor, decay: Optional[torch.Tensor] = None,
+                lower: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                sin: Optional[torch.Tensor] = None, rot_dims: int = 0, k_scale: float = 1.0) -> None:
+    """The recurrence S_t = diag(a_t) S_(t-1) + b_t v_t^T, o_t = S_t^T q_t per sequence and head over the step's
+    tokens, from ``state`` [slots, heads, head_dim, v_head_dim] (float32, updated when ``write_state``) to ``out``
+    [T, heads * v_head_dim] (float32).  q, k and v are column ranges of ``proj`` [T, ld].  ``SCAN_DECAY``: a = decay[h],
+    b = rotated k times ``k_scale``, q rotated (the first ``rot_dims`` dimensions, i paired with i + rot_dims / 2).
+    ``SCAN_GATED``: the k columns hold the gate's pre-activation z; a = lower + (1 - lower) sigmoid(z), b = 1 - a,
+    q = silu of the q columns."""
+    T = proj.shape[0]
+    assert state.dtype == out.dtype == torch.float32 and state.shape[1:] == (n_heads, head_dim, v_head_dim)
+    assert out.shape == (T, n_heads * v_head_dim) and proj.is_contiguous()
+    assert max(q_col, k_col) + n_heads * head_dim <= proj.shape[1] and v_col + n_heads * v_head_dim <= proj.shape[1]
+    if mode == SCAN_DECAY:
+        assert decay is not None and decay.dtype == torch.float32 and decay.numel() == n_heads
+        if rot_dims:
+            assert cos.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and sin.shape == cos.shape
+    else:
+        assert lower is not None and lower.dtype == torch.float32 and lower.numel() == n_heads * head_dim
+        rot_dims = 0
+    _check(lib().fd_linear_scan(_ptr(proj), proj.shape[1], _dt(proj.dtype), q_col, k_col, v_col, _ptr(state), _ptr(out),
+                                mode, _ptr(decay), _ptr(lower), _ptr(cos) if rot_dims else None,
+                                _ptr(sin) if rot_dims else None, cos.shape[0] if rot_dims else 0, rot_dims,
+                                float(k_scale), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
+                                n_rows, n_heads, head_dim, v_head_dim, int(write_state), _ptr(status), _stream()))
+
+
+def head_norm_gate(o: torch.Tensor, out: torch.Tensor, first_col: int, n_heads: int, v_head_dim: int, eps: float,
+                   weight: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_col: int = 0,
+                   scale: float = 1.0) -> None:
+    """out[t, first_col + h dv + j] = scale * o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) [* weight[j]]
+    [* silu(gate[t, gate_col + h dv + j])].  ``o`` float32 [T, heads * dv]; ``weight`` float32 [dv]; ``gate`` a packed
+    projection [T, ldg] in out's dtype."""
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.shape == (T, n_heads * v_head_dim) and out.shape[0] == T
+    assert first_col + n_heads * v_head_dim <= out.shape[1]
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == v_head_dim)
+    assert gate is None or (gate.dtype == out.dtype and gate.shape[0] == T and gate_col + n_heads * v_head_dim <= gate.shape[1])
+    _check(lib().fd_head_norm_gate(_ptr(o), _ptr(weight), _col_ptr(gate, gate_col) if gate is not None else None,
+                                   gate.shape[1] if gate is not None else 0, _col_ptr(out, first_col), out.shape[1],
+                                   _dt(out.dtype), T, n_heads, v_head_dim, float(eps), float(scale), _stream()))
+
+
 # ---------------------------------------------------------------------------
 # short convolution + partial rotation + cache append; gates; routed experts
 
@@ -683,38 +824,45 @@ def conv_rope_append(proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[t
                      cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dims: int, tok_row: torch.Tensor,
                      tok_pos: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int,
-                     head_dim: int, v_head_dim: int, write_kv: bool, update_state: bool, status: torch.Tensor) -> None:
+                     head_dim: int, v_head_dim: int, write_kv: bool, update_state: bool, status: torch.Tensor,
+                     interleaved: bool = False, first_col: int = 0) -> None:
     """For every token: the causal convolution over time of each q, k and v channel of ``proj``
     [T, >= C] (C = (n_q + n_kv) head_dim + n_kv v_head_dim leading columns) with ``conv_w`` [C, taps]
     (float32), earlier steps' values taken from ``state`` [slots, taps - 1, C] (float32); rotation of
     the first ``rot_dims`` dimensions of every q and k head (i paired with i + rot_dims / 2); q to
     ``q_out`` [T, n_q head_dim], k and v to the paged pools.  ``update_state``: rows that bring one
-    token move their state on in the same kernel (use ``conv_state_update`` for the others)."""
+    token move their state on in the same kernel (use ``conv_state_update`` for the others).
+    ``interleaved``: the rotation pairs dimension 2i with 2i + 1.  ``first_col``: the column of ``proj``
+    at which the C channels start (an even number)."""
     T = proj.shape[0]
     taps = conv_w.shape[1]
     C = (n_q + n_kv) * head_dim + n_kv * v_head_dim
-    assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and proj.shape[1] >= C
+    assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and proj.shape[1] >= first_col + C
+    assert first_col % 2 == 0 and proj.is_contiguous()
     assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C))
     assert proj.dtype == q_out.dtype == k_pool.dtype == v_pool.dtype and q_out.shape == (T, n_q * head_dim)
     assert k_pool.shape[-1] == head_dim and v_pool.shape[-1] == v_head_dim
     if rot_dims:
         assert cos.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and sin.shape == cos.shape
     num_blocks, _, block_size, _ = k_pool.shape
-    _check(lib().fd_conv_rope_append(_ptr(proj), proj.shape[1], _dt(proj.dtype), _ptr(conv_w), _ptr(state), _ptr(q_out),
+    _check(lib().fd_conv_rope_append(_ptr(proj) + first_col * proj.element_size(), proj.shape[1], _dt(proj.dtype),
+                                     _ptr(conv_w), _ptr(state), _ptr(q_out),
                                      _ptr(cos) if rot_dims else None, _ptr(sin) if rot_dims else None,
                                      cos.shape[0] if rot_dims else 0, rot_dims, _ptr(tok_row), _ptr(tok_pos),
                                      _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(k_pool), _ptr(v_pool),
                                      _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, n_q, n_kv,
                                      head_dim, v_head_dim, taps, int(write_kv), int(update_state), _ptr(status),
-                                     _stream()))
+                                     int(interleaved), _stream()))
 
 
 def conv_state_update(proj: torch.Tensor, state: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor,
-                      row_q_len: torch.Tensor, n_rows: int) -> None:
-    """``state`` [slots, taps - 1, C] of every row's sequence <- its last taps - 1 projected values after the step."""
+                      row_q_len: torch.Tensor, n_rows: int, first_col: int = 0) -> None:
+    """``state`` [slots, taps - 1, C] of every row's sequence <- its last taps - 1 projected values after the step
+    (the C columns of ``proj`` from ``first_col`` on)."""
     hist, C = state.shape[1], state.shape[2]
-    assert state.dtype == torch.float32 and proj.shape[1] >= C
-    _check(lib().fd_conv_state_update(_ptr(proj), proj.shape[1], _dt(proj.dtype), _ptr(state), _ptr(row_slot),
+    assert state.dtype == torch.float32 and proj.shape[1] >= first_col + C and proj.is_contiguous()
+    _check(lib().fd_conv_state_update(_ptr(proj) + first_col * proj.element_size(), proj.shape[1], _dt(proj.dtype),
+                                      _ptr(state), _ptr(row_slot),
                                       _ptr(row_q_start), _ptr(row_q_len), n_rows, C, hist + 1, _stream()))
 
 

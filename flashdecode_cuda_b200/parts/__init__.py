@@ -1,8 +1,8 @@
 """The parts a model is put together from.  Importing this package registers
 the parts of the architectures this library ships."""
 
-from . import (attention, block, conv_attention, embedding, head, lanes, mlp, moe, norm, normed_attention, rope,  # noqa: F401
-               stream)  # noqa: F401  (registration)
+from . import (attention, block, conv_attention, embedding, head, lanes, mlp, moe, norm, normed_attention,  # noqa: F401
+               parallel, recurrent, rope, stream)  # noqa: F401  (registration)
 from .base import (Block, Embedding, FeedForward, Head, KVRequest, LayerCache, Mixer, Norm, Part, Position,
                    Runtime)
 

@@ -58,17 +58,20 @@ class KVRequest:
     """Paged key/value storage a mixer needs for each sequence.  ``window``: only the last
     so many keys are ever read; ``chunk``: only the keys of the query's own chunk of so many
     positions; ``v_head_dim``: size of a value head where it differs from ``head_dim``; ``keys_only``: one
-    vector per position and head is kept and read both as key and as value."""
+    vector per position and head is kept and read both as key and as value; ``keep_first``: with a window, the
+    first so many positions stay readable for good."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     v_head_dim: Optional[int] = None
     keys_only: bool = False
+    keep_first: int = 0
 
     def key(self):
         v = None if self.v_head_dim in (None, self.head_dim) else self.v_head_dim
-        return (self.n_kv_heads, self.head_dim, self.window, self.chunk, v, self.keys_only)
+        keep = self.keep_first if self.window is not None else 0
+        return (self.n_kv_heads, self.head_dim, self.window, self.chunk, v, self.keys_only, keep)
 
 
 @dataclass

@@ -1,5 +1,7 @@
 """Attention whose q, k and v pass through a short causal convolution over time,
-with a partial rotation, chunked visibility and a sigmoid gate on the output."""
+with a partial rotation, chunked or windowed visibility and, by option, a sigmoid
+gate on the output, biased projections, capped scores, kept first positions, a
+keyless term in the softmax denominator and heads whose weights are mixed."""
 
 from __future__ import annotations
 
@@ -31,6 +33,14 @@ class ConvGatedAttention(Mixer):
     Visible keys of the query at position i: j <= i, of the last ``window`` positions if a window is given, and
     of i's own chunk (i // chunk == j // chunk) if a chunk is given.
 
+    Options: ``bias`` (q, k and v have biases ``.q.b`` / ``.k.b`` / ``.v.b``, added in the projection, before the
+    convolution); ``interleaved`` (the rotation pairs dimension 2i with 2i + 1 instead of i with i + rot_dims / 2);
+    ``softcap`` (score <- softcap * tanh(score / softcap) after scaling); ``keep_first`` (with a window, keys at
+    positions below it stay visible, at their true positions); ``sink`` (``.sink`` [heads]: exp(sink_h) is one more
+    term of head h's softmax denominator, with no key and no value); ``talk`` (``.talk`` [heads, heads]: after the
+    softmax the heads' weights are mixed, a'_h = sum_g talk[h, g] a_g, and head h applies a'_h to the values of its
+    own key/value head).  Scores, softmax, the sink and the mixing are float32 in both dtypes.
+
     The last ``taps - 1`` projected values (before the convolution) of every sequence are its state, kept in
     float32 per cache slot; keys (rotated) and values (both after the convolution) go to the paged cache.
     One packed product gives q, k, v and the gate.  Tensors: ``<prefix>.q`` / ``.k`` / ``.v`` / ``.g`` / ``.o``
@@ -39,7 +49,8 @@ class ConvGatedAttention(Mixer):
 
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
                  taps: int, scale: float, position=None, rot_dims: int = 0, chunk: Optional[int] = None,
-                 window: Optional[int] = None, gate: bool = True):
+                 window: Optional[int] = None, gate: bool = True, bias: bool = False, interleaved: bool = False,
+                 softcap: Optional[float] = None, keep_first: int = 0, sink: bool = False, talk: bool = False):
         for what, n in (("head size", head_dim), ("value head size", v_head_dim)):
             if n < 8 or n > 256 or n % 8 != 0:
                 raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take multiples of 8 "
@@ -54,6 +65,14 @@ class ConvGatedAttention(Mixer):
         self.hidden_size, self.n_q, self.n_kv, self.d, self.dv = hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim
         self.taps, self.scale, self.position, self.rot_dims = taps, float(scale), position, rot_dims
         self.chunk, self.window, self.gate = chunk, window, gate
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"{prefix}: the scores' soft cap must be positive, got {softcap}")
+        if keep_first < 0 or (talk and gate):
+            raise ValueError(f"{prefix}: keep_first must not be negative, and mixed heads take no gate")
+        self.bias, self.interleaved, self.softcap = bool(bias), bool(interleaved), softcap
+        self.keep_first, self.sink, self.talk = int(keep_first) if window else 0, bool(sink), bool(talk)
+        # the options only the CUDA-core attention kernel has
+        self.extended = bool(softcap or self.keep_first or sink or talk)
         self.n_conv = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim     # channels that are convolved
 
     # --- what it needs -------------------------------------------------
@@ -66,13 +85,19 @@ class ConvGatedAttention(Mixer):
         for n, c in self._sizes():
             specs.append(TensorSpec(f"{p}.{n}", (c, H), init="unit"))
             specs.append(TensorSpec(f"{p}.{n}.conv", (c, self.taps), "vector", init="conv"))
+            if self.bias:
+                specs.append(TensorSpec(f"{p}.{n}.b", (c,), "vector", init="bias"))
+        if self.sink:
+            specs.append(TensorSpec(f"{p}.sink", (self.n_q,), "vector", init="sink"))
+        if self.talk:
+            specs.append(TensorSpec(f"{p}.talk", (self.n_q, self.n_q), "vector", init="lane_mix"))
         if self.gate:
             specs.append(TensorSpec(f"{p}.g", (self.n_q * self.dv, H), init="unit"))
         specs.append(TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit"))
         return specs
 
     def kv_request(self) -> KVRequest:
-        return KVRequest(self.n_kv, self.d, self.window, self.chunk, self.dv)
+        return KVRequest(self.n_kv, self.d, self.window, self.chunk, self.dv, keep_first=self.keep_first)
 
     def state_requests(self) -> List[StateSpec]:
         if self.taps == 1:
@@ -86,49 +111,98 @@ class ConvGatedAttention(Mixer):
         if self.gate:
             mats.append(tensors.pop(f"{p}.g"))
         self.w_in = torch.cat(mats, dim=0).contiguous()            # [q | k | v | gate] rows: one product
+        self.b_in = None
+        if self.bias:
+            b = [tensors.pop(f"{p}.{n}.b").float() for n, _ in self._sizes()]
+            if self.gate:
+                b.append(torch.zeros(self.n_q * self.dv, dtype=torch.float32, device=b[0].device))
+            self.b_in = torch.cat(b).contiguous()
         self.conv_w = torch.cat([tensors.pop(f"{p}.{n}.conv").float() for n, _ in self._sizes()], dim=0).contiguous()
+        self.sink_w = tensors.pop(f"{p}.sink").float().contiguous() if self.sink else None
+        self.talk_w = tensors.pop(f"{p}.talk").float().contiguous() if self.talk else None
         self.w_o = tensors[f"{p}.o"]
 
     def weight_bytes(self) -> int:
-        return (self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
-                + self.conv_w.numel() * 4)
+        w_o = self.w_o.numel() * self.w_o.element_size() if self.w_o is not None else 0
+        return self.w_in.numel() * self.w_in.element_size() + w_o + self.conv_w.numel() * 4
 
     def first_weights(self) -> Optional[torch.Tensor]:
         return self.w_in
 
+    # --- as one of several mixers that share their input and output products (``parts.parallel``) ------------
+    @property
+    def shares_products(self) -> bool:
+        """Whether ``inner`` can leave its activations, scaled, in a column range of a wider buffer: with mixed
+        heads the mixing kernel is the one that writes them."""
+        return self.talk
+
+    def in_proj(self):
+        return self.w_in, self.b_in
+
+    def out_proj(self) -> torch.Tensor:
+        return self.w_o
+
     # --- a step ----------------------------------------------------------
-    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+    def inner(self, ctx, proj: torch.Tensor, col0: int, lc: LayerCache, act: Optional[torch.Tensor] = None,
+              act_col: int = 0, scale: float = 1.0) -> torch.Tensor:
+        """From this mixer's columns of ``proj`` (starting at ``col0``) to the input of its output product.  With
+        ``act`` given (mixed heads only) that is written, times ``scale``, into act[:, act_col:]; else returned."""
         T, ws, rt = ctx.T, ctx.ws, self.rt
-        proj = ws.get("cga_proj", (T, self.w_in.shape[0]), x.dtype)
-        matmul(x, self.w_in, None, proj, status=rt.status)
-        q = ws.get("cga_q", (T, self.n_q * self.d), x.dtype)
+        dt = proj.dtype
+        q = ws.get("cga_q", (T, self.n_q * self.d), dt)
         state = lc.states.get("conv")
         rope = self.position
         single = ctx.max_q_len == 1                     # every row brings one token: the state moves on in the same kernel
         K.conv_rope_append(proj, self.conv_w, state, q, rope.cos if self.rot_dims else None,
                            rope.sin if self.rot_dims else None, self.rot_dims, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                            ctx.row_q_start, ctx.row_q_len, lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv,
-                           self.d, self.dv, lc.writes, single and lc.writes, rt.status)
+                           self.d, self.dv, lc.writes, single and lc.writes, rt.status, interleaved=self.interleaved,
+                           first_col=col0)
         if state is not None and lc.writes and not single:
-            K.conv_state_update(proj, state, ctx.row_slot, ctx.row_q_start, ctx.row_q_len, ctx.n_rows)
-        attn = ws.get("cga_attn", (T, self.n_q * self.dv), x.dtype)
+            K.conv_state_update(proj, state, ctx.row_slot, ctx.row_q_start, ctx.row_q_len, ctx.n_rows, first_col=col0)
+        heads_out = self.n_q * (self.n_kv if self.talk else 1)      # mixed heads: every head's weights on every value head
         n_splits, split_len, scratch = 1, 0, None
         if single:
-            if x.dtype == torch.float32:
+            if dt == torch.float32:
                 # splits of a fixed length: where a sequence's partial sums are cut depends on its own length only
                 split_len = FP32_SPLIT_LEN
                 n_splits = max(1, -(-ctx.kv_len_bound // split_len))
             else:
-                n_splits, split_len = plan_splits(ctx.n_rows, self.n_kv, ctx.kv_len_bound, rt.sm_count)
+                n_splits, split_len = plan_splits(ctx.n_rows, heads_out // (self.n_q // self.n_kv), ctx.kv_len_bound,
+                                                  rt.sm_count)
             if n_splits > 1:
-                scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, self.dv, n_splits),),
+                scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, heads_out, self.dv, n_splits),),
                                  torch.float32)
-        K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
-                    ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
-                    self.window or 0, n_splits, split_len, scratch, rt.status, chunk=self.chunk or 0)
+        if not self.extended:
+            attn = ws.get("cga_attn", (T, self.n_q * self.dv), dt)
+            K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
+                        ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d, self.scale,
+                        self.window or 0, n_splits, split_len, scratch, rt.status, chunk=self.chunk or 0)
+        else:
+            attn = ws.get("cga_attn_f" if self.talk else "cga_attn", (T, heads_out * self.dv),
+                          torch.float32 if self.talk else dt)
+            K.attention_ext(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot, ctx.row_q_start,
+                            ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len, self.n_q, self.n_kv, self.d,
+                            self.scale, self.window or 0, n_splits, split_len, scratch, rt.status, chunk=self.chunk or 0,
+                            softcap=self.softcap or 0.0, keep_first=self.keep_first, sink=self.sink_w,
+                            all_value_heads=self.talk)
+        if self.talk:
+            if act is None:
+                act, act_col = ws.get("cga_mixed", (T, self.n_q * self.dv), dt), 0
+            K.attn_head_mix(attn, self.talk_w, act, act_col, self.n_q, self.n_kv, self.dv, scale)
+            return act
+        if act is not None:
+            raise ValueError(f"{self.prefix}: without mixed heads this mixer keeps its own output product")
         if self.gate:
-            gated = ws.get("cga_gated", (T, self.n_q * self.dv), x.dtype)
-            K.gate_mul(attn, proj, self.n_conv, gated)
+            gated = ws.get("cga_gated", (T, self.n_q * self.dv), dt)
+            K.gate_mul(attn, proj, col0 + self.n_conv, gated)
             attn = gated
+        return attn
+
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        proj = ws.get("cga_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, self.b_in, proj, status=rt.status)
+        attn = self.inner(ctx, proj, 0, lc)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
         return matmul(attn, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status)

@@ -19,15 +19,16 @@ class LinearHead(Head):
     of davidjoyme/flashdecode-cuda).  ``tied_to``: the name of the embedding
     table to use when the checkpoint keeps no separate head
     (engine/loader.py:39-40).  ``softcap``: the logits are squashed to
-    softcap * tanh(logits / softcap)."""
+    softcap * tanh(logits / softcap).  ``scale``: the logits are multiplied by it (in float32, before any cap)."""
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
-                 tensor: Optional[str] = None, softcap: Optional[float] = None):
+                 tensor: Optional[str] = None, softcap: Optional[float] = None, scale: Optional[float] = None):
         self.name = tensor or f"{prefix}.weight"        # ``tensor``: the matrix's full name where it is not <prefix>.weight
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to
         if softcap is not None and not softcap > 0:
             raise ValueError(f"the logits' soft cap must be positive, got {softcap}")
         self.softcap = softcap
+        self.scale = None if scale is None or float(scale) == 1.0 else float(scale)
 
     def tensor_specs(self) -> List[TensorSpec]:
         if self.tied_to:
@@ -47,6 +48,8 @@ class LinearHead(Head):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         logits = ctx.ws.get("logits", (x.shape[0], self.vocab_size), torch.float32)
         matmul(x, self.weight, None, logits, status=self.rt.status)
+        if self.scale is not None:
+            K.scale_(logits, self.scale)
         if self.softcap is not None:
             K.softcap(logits, self.softcap)
         return logits

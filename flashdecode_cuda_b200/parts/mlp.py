@@ -1,4 +1,4 @@
-"""Dense gated feed-forward (SwiGLU)."""
+"""Dense feed-forwards: gated (SwiGLU and its relatives) and plain with a parametric activation."""
 
 from __future__ import annotations
 
@@ -145,4 +145,47 @@ class GatedMLP(FeedForward):
             K.glu_mul(gu, act, self.kind, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
         return matmul(act, self.w_down, self.b_down, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status,
+                      upcoming=ctx.upcoming)
+
+
+@register_part("feed_forward", "dense_act")
+class DenseActMLP(FeedForward):
+    """down( act(up(x)) ), no gate and no biases, with the two-parameter activation ``quad_exp``:
+
+        act(z) = softplus(p) z^2 + z / 2                          for z > 0
+                 (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2     for z <= 0
+
+    (p, q) are the tensor ``<prefix>.act`` [2].  Tensors ``<prefix>.up`` / ``.down`` (stored [out, in]).  The
+    activation is computed in float32 and rounded once."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "quad_exp"):
+        if activation != "quad_exp":
+            raise ValueError(f"{prefix}: unknown activation {activation!r}; known: quad_exp")
+        self.prefix, self.hidden_size, self.inter, self.activation = prefix, hidden_size, intermediate_size, activation
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.inter
+        return [TensorSpec(f"{p}.up", (I, H), init="unit"), TensorSpec(f"{p}.down", (H, I), init="unit"),
+                TensorSpec(f"{p}.act", (2,), "vector", init="half")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_up, self.w_down = tensors[f"{p}.up"], tensors[f"{p}.down"]
+        self.pq = tensors.pop(f"{p}.act").float().contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_up
+
+    def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
+        T, ws = ctx.T, ctx.ws
+        up = ws.get("ffn_up", (T, self.inter), x.dtype)
+        matmul(x, self.w_up, None, up, status=self.rt.status)
+        act = ws.get("ffn_act", (T, self.inter), x.dtype)
+        K.quad_exp_act(up, self.pq, act)
+        out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
+        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status,
                       upcoming=ctx.upcoming)

@@ -1,4 +1,4 @@
-"""RMSNorm fused with the deferred residual add."""
+"""Norms fused with the deferred residual add: RMSNorm and Dynamic Tanh."""
 
 from __future__ import annotations
 
@@ -47,3 +47,34 @@ class RMSNorm(Norm):
                 write_resid: bool = True, n_parts: int = 1) -> None:
         K.add_rmsnorm(delta, resid, self.weight, self.eps, out, rows=rows, n_out=n_out,
                       write_resid=write_resid, n_parts=n_parts)
+
+
+@register_part("norm", "dyn_tanh")
+class DynTanh(Norm):
+    """resid += delta; out = tanh(alpha * resid) * weight + bias, with a learned scalar alpha: a norm that computes no
+    mean and no variance.  Tensors ``<tensor>`` (weight), ``<tensor>.b`` and ``<tensor>.alpha`` (a scalar).  The sum,
+    the tanh and the affine map are float32 in both dtypes; weight and bias are kept in float32."""
+
+    def __init__(self, prefix: str, size: int, tensor: Optional[str] = None, optional: bool = False):
+        self.name = tensor or f"{prefix}.weight"
+        self.size, self.optional = size, bool(optional)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.size,), "vector", optional=self.optional, init="norm"),
+                TensorSpec(f"{self.name}.b", (self.size,), "vector", optional=self.optional, init="bias"),
+                TensorSpec(f"{self.name}.alpha", (), "vector", optional=self.optional, init="half")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.weight = self.bias = None
+        self.alpha = 1.0
+        if self.name in tensors:
+            self.weight = tensors[self.name].float().contiguous()
+            self.bias = tensors[f"{self.name}.b"].float().contiguous()
+            self.alpha = float(tensors[f"{self.name}.alpha"].float().item())     # a kernel argument from now on
+
+    def forward(self, ctx, delta: Optional[torch.Tensor], resid: torch.Tensor, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,
+                write_resid: bool = True, n_parts: int = 1) -> None:
+        K.add_dyn_tanh(delta, resid, self.weight, self.bias, self.alpha, out, rows=rows, n_out=n_out,
+                       write_resid=write_resid)

@@ -1,0 +1,151 @@
+"""Mixers that carry a matrix state per head instead of keys: linear attention with a constant decay per head
+(retention) and with a forget gate per channel that also decides what is written (a gated linear recurrence)."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import kernels as K
+from ..cache.paged import StateSpec
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .base import LayerCache, Mixer, Runtime
+from .linear import matmul
+
+
+class _StateMixer(Mixer):
+    """What the two recurrences share: a state [heads, head_dim, v_head_dim] in float32 per cache slot, one packed
+    input product, and the protocol by which several mixers share their input and output products."""
+
+    shares_products = True
+
+    def kv_request(self):
+        return None
+
+    def state_requests(self) -> List[StateSpec]:
+        return [StateSpec("state", (self.n_heads, self.d, self.dv), torch.float32)]
+
+    def weight_bytes(self) -> int:
+        w_o = self.w_o.numel() * self.w_o.element_size() if self.w_o is not None else 0
+        return self.w_in.numel() * self.w_in.element_size() + w_o
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_in
+
+    def in_proj(self):
+        return self.w_in, self.b_in
+
+    def out_proj(self) -> torch.Tensor:
+        return self.w_o
+
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        proj = ws.get("rec_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, self.b_in, proj, status=rt.status)
+        act = ws.get("rec_act", (T, self.n_heads * self.dv), x.dtype)
+        self.inner(ctx, proj, 0, lc, act, 0, 1.0)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        return matmul(act, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status, upcoming=ctx.upcoming)
+
+
+@register_part("mixer", "retention")
+class Retention(_StateMixer):
+    """For the mixer's input h [T, hidden], per head with the constant decay g_h:
+
+        q, k = rot(W_q h), rot(W_k h) * head_dim^(-1/2);  v = W_v h          (no biases)
+        S_t  = g_h S_(t-1) + k_t v_t^T;   o_t = S_t^T q_t                  (no softmax, no denominator)
+        out  = W_o ( concat_h o_t / rms(o_t) * silu(W_g h) )               (rms over a head's ``v_head_dim``, with eps)
+
+    rot turns the first ``rot_dims`` dimensions of every head at the token's position, dimension i paired with
+    i + rot_dims / 2.  The state starts at zero and is carried in float32 per cache slot; rotation, decay, state,
+    output and the norm are float32 in both dtypes.  Tensors ``<prefix>.q`` / ``.k`` / ``.v`` / ``.g`` / ``.o``."""
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int,
+                 decay: Sequence[float], eps: float, position=None, rot_dims: int = 0):
+        if len(decay) != n_heads:
+            raise ValueError(f"{prefix}: {len(decay)} decays for {n_heads} heads")
+        if head_dim > 256 or min(n_heads, head_dim, v_head_dim) < 1:
+            raise ValueError(f"{prefix}: heads of {head_dim} x {v_head_dim}: the recurrence takes key sizes up to 256")
+        if rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim or (rot_dims and position is None):
+            raise ValueError(f"{prefix}: {rot_dims} rotated dimensions of {head_dim}")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.n_heads, self.d, self.dv = n_heads, head_dim, v_head_dim
+        self.decay, self.eps, self.position, self.rot_dims = [float(g) for g in decay], float(eps), position, rot_dims
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        return [TensorSpec(f"{p}.q", (nk, H), init="unit"), TensorSpec(f"{p}.k", (nk, H), init="unit"),
+                TensorSpec(f"{p}.v", (nv, H), init="unit"), TensorSpec(f"{p}.g", (nv, H), init="unit"),
+                TensorSpec(f"{p}.o", (H, nv), init="unit")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n in "qkvg"], dim=0).contiguous()
+        self.b_in = None
+        self.w_o = tensors[f"{p}.o"]
+        self.decay_dev = torch.tensor(self.decay, dtype=torch.float32, device=rt.device)
+
+    def inner(self, ctx, proj: torch.Tensor, col0: int, lc: LayerCache, act: torch.Tensor, act_col: int = 0,
+              scale: float = 1.0) -> torch.Tensor:
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        o = ctx.ws.get("scan_out", (ctx.T, nv), torch.float32)
+        rope = self.position
+        K.linear_scan(proj, col0, col0 + nk, col0 + 2 * nk, lc.states["state"], o, K.SCAN_DECAY, ctx.row_slot,
+                      ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv,
+                      lc.writes, self.rt.status, decay=self.decay_dev, cos=rope.cos if self.rot_dims else None,
+                      sin=rope.sin if self.rot_dims else None, rot_dims=self.rot_dims, k_scale=self.d ** -0.5)
+        K.head_norm_gate(o, act, act_col, self.n_heads, self.dv, self.eps, None, proj, col0 + 2 * nk + nv, scale)
+        return act
+
+
+@register_part("mixer", "gated_linear_recurrence")
+class GatedLinearRecurrence(_StateMixer):
+    """For the mixer's input h [T, hidden], per head:
+
+        q = silu(W_q h);  v = W_v h;  f = lower + (1 - lower) * sigmoid(W_f h + b_f)     (per channel of q)
+        S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T;   o_t = S_t^T q_t                     (no key, no other scale)
+        out = W_o ( concat_h o_t / rms(o_t) * w )                                        (w [v_head_dim], shared by heads)
+
+    The state starts at zero and is carried in float32 per cache slot; gate, state, output and the norm are float32 in
+    both dtypes.  Tensors ``<prefix>.q`` / ``.f`` / ``.f.b`` / ``.lower`` / ``.v`` / ``.norm`` / ``.o``."""
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int, eps: float):
+        if head_dim > 256 or min(n_heads, head_dim, v_head_dim) < 1:
+            raise ValueError(f"{prefix}: heads of {head_dim} x {v_head_dim}: the recurrence takes key sizes up to 256")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.n_heads, self.d, self.dv, self.eps = n_heads, head_dim, v_head_dim, float(eps)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        return [TensorSpec(f"{p}.q", (nk, H), init="unit"), TensorSpec(f"{p}.f", (nk, H), init="unit"),
+                TensorSpec(f"{p}.f.b", (nk,), "vector", init="bias"),
+                TensorSpec(f"{p}.lower", (nk,), "vector", init="unit_interval"),
+                TensorSpec(f"{p}.v", (nv, H), init="unit"), TensorSpec(f"{p}.norm", (self.dv,), "vector", init="norm"),
+                TensorSpec(f"{p}.o", (H, nv), init="unit")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n in "qfv"], dim=0).contiguous()
+        fb = tensors.pop(f"{p}.f.b").float()
+        self.b_in = torch.cat([torch.zeros(nk, dtype=torch.float32, device=fb.device), fb,
+                               torch.zeros(nv, dtype=torch.float32, device=fb.device)]).contiguous()
+        self.lower = tensors.pop(f"{p}.lower").float().contiguous()
+        self.norm_w = tensors.pop(f"{p}.norm").float().contiguous()
+        self.w_o = tensors[f"{p}.o"]
+
+    def inner(self, ctx, proj: torch.Tensor, col0: int, lc: LayerCache, act: torch.Tensor, act_col: int = 0,
+              scale: float = 1.0) -> torch.Tensor:
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        o = ctx.ws.get("scan_out", (ctx.T, nv), torch.float32)
+        K.linear_scan(proj, col0, col0 + nk, col0 + 2 * nk, lc.states["state"], o, K.SCAN_GATED, ctx.row_slot,
+                      ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv,
+                      lc.writes, self.rt.status, lower=self.lower)
+        K.head_norm_gate(o, act, act_col, self.n_heads, self.dv, self.eps, self.norm_w, None, 0, scale)
+        return act

@@ -111,6 +111,12 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
             t = 1.0 / spec.shape[0] + 0.1 * t
         elif spec.init == "lane_mix":           # a lane mixing matrix: about the unit matrix
             t = torch.eye(spec.shape[0], dtype=torch.float32, device=device) + 0.1 * t
+        elif spec.init == "half":               # a positive scalar or pair of about one half
+            t = 0.5 + 0.1 * t
+        elif spec.init == "sink":               # a keyless softmax term of about the size of a score
+            t = 0.5 * t
+        elif spec.init == "unit_interval":      # lower bounds of a gate: inside (0, 1)
+            t = torch.sigmoid(t)
         elif spec.init in ("normal", "bias", "embedding"):
             t = 0.02 * t
         else:

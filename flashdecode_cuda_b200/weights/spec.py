@@ -16,7 +16,8 @@ class TensorSpec:
     ``init``: how the random-weights mode draws it: ``normal`` N(0, 0.02),
     ``norm`` 1 + N(0, 0.1), ``norm_zero`` N(0, 0.1), ``conv`` N(0, 0.5), ``unit``
     N(0, 1 / fan-in) (products that keep their input's scale), ``bias`` N(0, 0.02),
-    ``lane_read`` 1 / n + N(0, 0.1), ``lane_mix`` the unit matrix + N(0, 0.1), ``zeros``."""
+    ``lane_read`` 1 / n + N(0, 0.1), ``lane_mix`` the unit matrix + N(0, 0.1), ``half`` 0.5 + N(0, 0.1),
+    ``sink`` N(0, 0.5), ``unit_interval`` sigmoid(N(0, 1)), ``zeros``."""
 
     name: str
     shape: Tuple[int, ...]
