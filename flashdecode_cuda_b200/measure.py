@@ -20,7 +20,9 @@ from . import kernels as K
 LAUNCHERS = ["embed", "add_rmsnorm", "silu_mul", "rope_append", "gemv_qkv_rope", "gemm_tc_qkv_rope", "gemm_tc",
              "gemm_stream", "gemm_stream_qkv_rope", "gemv", "gemm_simt", "attention", "conv_rope_append",
              "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine",
-             "moe_gather", "gemm_tc_grouped", "glu_mul", "softcap", "lanes_norm", "lanes_fill", "norm_append", "head_gemm"]
+             "moe_gather", "gemm_tc_grouped", "glu_mul", "softcap", "lanes_norm", "lanes_fill", "norm_append", "head_gemm",
+             "attention_ext", "attn_head_mix", "add_dyn_tanh", "quad_exp_act", "scale_", "axpy_f32", "linear_scan",
+             "head_norm_gate"]
 
 
 class PartTimer:
@@ -98,8 +100,10 @@ class PartTimer:
         return {lab: {k: (v[0], v[1]) for k, v in d.items()} for lab, d in out.items()}
 
 
-def visible_pairs(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Optional[int], chunk: Optional[int]) -> int:
-    """(query, key) pairs a causal attention with a window and / or chunks evaluates in a step."""
+def visible_pairs(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Optional[int], chunk: Optional[int],
+                  keep_first: int = 0) -> int:
+    """(query, key) pairs a causal attention with a window (which may keep the first positions) and / or chunks
+    evaluates in a step."""
     total = 0
     for c, n in zip(ctx_lens, q_lens):
         for i in range(c, c + n):
@@ -108,12 +112,14 @@ def visible_pairs(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Option
                 first = max(first, i - window + 1)
             if chunk:
                 first = max(first, (i // chunk) * chunk)
-            total += i + 1 - first
+            total += i + 1 - first + (min(keep_first, first) if window else 0)
     return total
 
 
-def keys_read(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Optional[int], chunk: Optional[int]) -> int:
-    """Cached positions a step has to read at least once: per row, from the first key its first query sees."""
+def keys_read(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Optional[int], chunk: Optional[int],
+              keep_first: int = 0) -> int:
+    """Cached positions a step has to read at least once: per row, from the first key its first query sees (and the
+    kept first positions)."""
     total = 0
     for c, n in zip(ctx_lens, q_lens):
         first = 0
@@ -121,7 +127,7 @@ def keys_read(ctx_lens: Sequence[int], q_lens: Sequence[int], window: Optional[i
             first = max(first, c - window + 1)
         if chunk:
             first = max(first, (c // chunk) * chunk)
-        total += c + n - first
+        total += c + n - first + (min(keep_first, first) if window else 0)
     return total
 
 
@@ -143,11 +149,35 @@ def part_work(part, ctx_lens: Sequence[int], q_lens: Sequence[int], real_choice_
         kv = keys_read(ctx_lens, q_lens, part.window, part.chunk) * n_kv * 2 * d * el
         return float(flops), float(part.weight_bytes() + kv + act)
     if name == "ConvGatedAttention":
-        n_q, n_kv, d, dv = part.n_q, part.n_kv, part.d, part.dv
-        pairs = visible_pairs(ctx_lens, q_lens, part.window, part.chunk)
-        flops = 2 * T * H * part.w_in.shape[0] + 2 * T * n_q * dv * H + 2 * n_q * (d + dv) * pairs
-        kv = keys_read(ctx_lens, q_lens, part.window, part.chunk) * n_kv * (d + dv) * el
-        return float(flops), float(part.weight_bytes() + kv + act)
+        flops, byt = _conv_attention_inner(part, ctx_lens, q_lens, el)
+        n_q, dv = part.n_q, part.dv
+        return float(flops + 2 * T * H * part.w_in.shape[0] + 2 * T * n_q * dv * H), float(part.weight_bytes() + byt + act)
+    if name in ("Retention", "GatedLinearRecurrence"):
+        flops, byt = _recurrence_inner(part, q_lens)
+        nv = part.n_heads * part.dv
+        return float(flops + 2 * T * H * part.w_in.shape[0] + 2 * T * nv * H), float(part.weight_bytes() + byt + act)
+    if name == "ParallelMixers":
+        # the branches' inner work, and their input and output products once each over the stacked matrices
+        flops, byt = 0.0, 0.0
+        for b in part.branches:
+            if type(b).__name__ == "ConvGatedAttention":
+                f, y = _conv_attention_inner(b, ctx_lens, q_lens, el)
+            elif type(b).__name__ in ("Retention", "GatedLinearRecurrence"):
+                f, y = _recurrence_inner(b, q_lens)
+            else:
+                f, y = part_work(b, ctx_lens, q_lens)
+                y -= act
+            flops, byt = flops + f, byt + y
+            if not part.fused:
+                flops += 2 * T * H * (b.w_in.shape[0] + b.w_o.shape[1])
+        if part.fused:
+            flops += 2 * T * H * (part.w_in.shape[0] + part.w_o.shape[1])
+            byt += (part.w_in.numel() + part.w_o.numel()) * el
+        else:
+            byt += sum(b.weight_bytes() for b in part.branches)
+        return float(flops), float(byt + act)
+    if name == "DenseActMLP":
+        return float(2 * T * 2 * H * part.inter), float(part.weight_bytes() + act)
     if name == "QKNormedAttention":
         n_q, n_kv, d, dv = part.n_q, part.n_kv, part.d, part.dv
         pairs = visible_pairs(ctx_lens, q_lens, part.window, None)
@@ -175,6 +205,23 @@ def part_work(part, ctx_lens: Sequence[int], q_lens: Sequence[int], real_choice_
         byt = (part.E + part.n_identity) * H * el + 2 * H * sff * el + touched * mats * H * part.ff * el + act
         return float(flops), float(byt)
     raise ValueError(f"no work model for a {name}")
+
+
+def _conv_attention_inner(part, ctx_lens, q_lens, el: int) -> Tuple[float, float]:
+    """(operations, bytes) of a convolved attention between its two products: scores and weighted values per visible
+    pair and query head, the cached keys and values the step has to read."""
+    n_q, n_kv, d, dv = part.n_q, part.n_kv, part.d, part.dv
+    keep = getattr(part, "keep_first", 0)
+    pairs = visible_pairs(ctx_lens, q_lens, part.window, part.chunk, keep)
+    kv = keys_read(ctx_lens, q_lens, part.window, part.chunk, keep) * n_kv * (d + dv) * el
+    return float(2 * n_q * (d + dv) * pairs), float(kv)
+
+
+def _recurrence_inner(part, q_lens) -> Tuple[float, float]:
+    """(operations, bytes) of a matrix-state recurrence between its two products: per token and state element one
+    multiply-add to move the state on and one to read it; every row's float32 state read and written once."""
+    elements = part.n_heads * part.d * part.dv
+    return float(4 * sum(q_lens) * elements), float(2 * len(q_lens) * elements * 4)
 
 
 def routing_of(model, n_tokens: int, top: int, n_experts: int) -> Tuple[float, int]:

@@ -16,6 +16,7 @@ from ..weights.spec import TensorSpec
 from .attention import FP32_SPLIT_LEN, plan_splits
 from .base import KVRequest, LayerCache, Mixer, Runtime
 from .linear import matmul
+from .normed_attention import _pad_heads, _up8
 
 
 @register_part("mixer", "conv_gated_attention")
@@ -52,9 +53,8 @@ class ConvGatedAttention(Mixer):
                  window: Optional[int] = None, gate: bool = True, bias: bool = False, interleaved: bool = False,
                  softcap: Optional[float] = None, keep_first: int = 0, sink: bool = False, talk: bool = False):
         for what, n in (("head size", head_dim), ("value head size", v_head_dim)):
-            if n < 8 or n > 256 or n % 8 != 0:
-                raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take multiples of 8 "
-                                 f"from 8 to 256")
+            if n < 1 or _up8(n) > 256:
+                raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take sizes from 1 to 256")
         if n_kv_heads < 1 or n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 64:
             raise ValueError(f"{prefix}: {n_heads} query heads for {n_kv_heads} key/value heads: the kernels take whole "
                              f"groups of up to 64 query heads per key/value head")
@@ -62,7 +62,11 @@ class ConvGatedAttention(Mixer):
             raise ValueError(f"{prefix}: {taps} taps, {rot_dims} rotated dimensions of {head_dim}: taps must be "
                              f"positive, the rotated dimensions even, at most the head size and given a position part")
         self.prefix = prefix
-        self.hidden_size, self.n_q, self.n_kv, self.d, self.dv = hidden_size, n_heads, n_kv_heads, head_dim, v_head_dim
+        # the kernels see head sizes that are multiples of 8: other sizes are padded with zero rows of the projections,
+        # biases and convolution weights (and zero columns of the output matrix) when the weights are bound, which
+        # changes no score and no output
+        self.d_true, self.dv_true = head_dim, v_head_dim
+        self.hidden_size, self.n_q, self.n_kv, self.d, self.dv = hidden_size, n_heads, n_kv_heads, _up8(head_dim), _up8(v_head_dim)
         self.taps, self.scale, self.position, self.rot_dims = taps, float(scale), position, rot_dims
         self.chunk, self.window, self.gate = chunk, window, gate
         if softcap is not None and not softcap > 0:
@@ -73,11 +77,18 @@ class ConvGatedAttention(Mixer):
         self.keep_first, self.sink, self.talk = int(keep_first) if window else 0, bool(sink), bool(talk)
         # the options only the CUDA-core attention kernel has
         self.extended = bool(softcap or self.keep_first or sink or talk)
-        self.n_conv = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim     # channels that are convolved
+        self.n_conv = (n_heads + n_kv_heads) * self.d + n_kv_heads * self.dv     # channels that are convolved
 
     # --- what it needs -------------------------------------------------
     def _sizes(self):
-        return (("q", self.n_q * self.d), ("k", self.n_kv * self.d), ("v", self.n_kv * self.dv))
+        """(tensor, channels as stored) of the three convolved projections."""
+        return (("q", self.n_q * self.d_true), ("k", self.n_kv * self.d_true), ("v", self.n_kv * self.dv_true))
+
+    def _padded(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        """A tensor whose rows are the channels of q, k or v, with zero rows up to the padded head size."""
+        heads, size, padded = {"q": (self.n_q, self.d_true, self.d), "k": (self.n_kv, self.d_true, self.d),
+                               "v": (self.n_kv, self.dv_true, self.dv)}[name]
+        return _pad_heads(t, heads, size, padded)
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H = self.prefix, self.hidden_size
@@ -92,8 +103,8 @@ class ConvGatedAttention(Mixer):
         if self.talk:
             specs.append(TensorSpec(f"{p}.talk", (self.n_q, self.n_q), "vector", init="lane_mix"))
         if self.gate:
-            specs.append(TensorSpec(f"{p}.g", (self.n_q * self.dv, H), init="unit"))
-        specs.append(TensorSpec(f"{p}.o", (H, self.n_q * self.dv), init="unit"))
+            specs.append(TensorSpec(f"{p}.g", (self.n_q * self.dv_true, H), init="unit"))
+        specs.append(TensorSpec(f"{p}.o", (H, self.n_q * self.dv_true), init="unit"))
         return specs
 
     def kv_request(self) -> KVRequest:
@@ -107,20 +118,23 @@ class ConvGatedAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
-        mats = [tensors.pop(f"{p}.{n}") for n, _ in self._sizes()]
+        mats = [self._padded(n, tensors.pop(f"{p}.{n}")) for n, _ in self._sizes()]
         if self.gate:
-            mats.append(tensors.pop(f"{p}.g"))
+            mats.append(_pad_heads(tensors.pop(f"{p}.g"), self.n_q, self.dv_true, self.dv))
         self.w_in = torch.cat(mats, dim=0).contiguous()            # [q | k | v | gate] rows: one product
         self.b_in = None
         if self.bias:
-            b = [tensors.pop(f"{p}.{n}.b").float() for n, _ in self._sizes()]
+            b = [self._padded(n, tensors.pop(f"{p}.{n}.b").float()) for n, _ in self._sizes()]
             if self.gate:
                 b.append(torch.zeros(self.n_q * self.dv, dtype=torch.float32, device=b[0].device))
             self.b_in = torch.cat(b).contiguous()
-        self.conv_w = torch.cat([tensors.pop(f"{p}.{n}.conv").float() for n, _ in self._sizes()], dim=0).contiguous()
+        self.conv_w = torch.cat([self._padded(n, tensors.pop(f"{p}.{n}.conv").float()) for n, _ in self._sizes()],
+                                dim=0).contiguous()
         self.sink_w = tensors.pop(f"{p}.sink").float().contiguous() if self.sink else None
         self.talk_w = tensors.pop(f"{p}.talk").float().contiguous() if self.talk else None
         self.w_o = tensors[f"{p}.o"]
+        if self.dv != self.dv_true:         # zero columns where the padded value dimensions arrive
+            self.w_o = _pad_heads(tensors.pop(f"{p}.o").t().contiguous(), self.n_q, self.dv_true, self.dv).t().contiguous()
 
     def weight_bytes(self) -> int:
         w_o = self.w_o.numel() * self.w_o.element_size() if self.w_o is not None else 0

@@ -120,21 +120,24 @@ def window_visible(i: int, j: int, size: int, keep_first: int) -> bool:
     return j <= i and (i - j < size or j < keep_first)
 
 
-def mixed_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, softcap: float, size: int,
-                         keep_first: int, sink: torch.Tensor, talk: torch.Tensor) -> torch.Tensor:
+def mixed_head_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, softcap: Optional[float],
+                         size: Optional[int], keep_first: int, sink: torch.Tensor, talk: torch.Tensor) -> torch.Tensor:
     """q [S, H, d], k [S, G, d], v [S, G, dv] -> [S, H, dv].  Head h scores against key head h // (H/G); scores are
     scaled, then capped to softcap * tanh(score / softcap); invisible keys drop out; the softmax denominator of head h
     also holds exp(sink[h]); after that the weights of the heads are mixed, w'_h = sum_g talk[h, g] w_g, and head h
-    applies w'_h to the values of ITS key/value head."""
+    applies w'_h to the values of ITS key/value head.  ``softcap`` None: no cap; ``size`` None: no window."""
     S, H, d = q.shape
     G = k.shape[1]
     per = H // G
     kk = k.repeat_interleave(per, dim=1)                           # [S, H, d]
     s = torch.einsum("ihd,jhd->hij", q, kk) * scale
-    s = softcap * torch.tanh(s / softcap)
+    if softcap is not None:
+        s = softcap * torch.tanh(s / softcap)
     i = torch.arange(S)[:, None]
     j = torch.arange(S)[None, :]
-    vis = (j <= i) & ((i - j < size) | (j < keep_first))
+    vis = j <= i
+    if size is not None:
+        vis = vis & ((i - j < size) | (j < keep_first))
     s = s.masked_fill(~vis[None], float("-inf"))
     m = torch.maximum(s.max(-1).values, sink[:, None])             # [H, S]
     e = torch.exp(s - m[:, :, None])
@@ -183,7 +186,8 @@ def left_branch(W, p: str, m: dict, h: torch.Tensor, dt=torch.float64) -> torch.
     S = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q, k, v = (_lin(W, f"{p}.{n}", h, dt, bias=True) for n in "qkv")
-    q, k, v = (short_conv(u, W[f"{p}.{n}.conv"].to(dt)) for n, u in (("q", q), ("k", k), ("v", v)))
+    if m.get("conv", 1) > 1 or f"{p}.q.conv" in W:
+        q, k, v = (short_conv(u, W[f"{p}.{n}.conv"].to(dt)) for n, u in (("q", q), ("k", k), ("v", v)))
     q, k, v = q.view(S, H, d), k.view(S, G, d), v.view(S, G, dv)
     rot = m.get("rot")
     if rot:
@@ -191,7 +195,8 @@ def left_branch(W, p: str, m: dict, h: torch.Tensor, dt=torch.float64) -> torch.
         pos = torch.arange(S)
         q = rotate(q, pos, rot["dims"], fr, mag, interleaved=True)
         k = rotate(k, pos, rot["dims"], fr, mag, interleaved=True)
-    a = mixed_head_attention(q, k, v, m["scale"], m["softcap"], m["mask"]["size"], m["mask"]["keep_first"],
+    mask = m.get("mask") or {}
+    a = mixed_head_attention(q, k, v, m["scale"], m.get("softcap"), mask.get("size"), mask.get("keep_first", 0),
                              W[f"{p}.sink"].to(dt), W[f"{p}.talk"].to(dt))
     return a.reshape(S, H * dv) @ W[f"{p}.o"].to(dt).t()
 
@@ -208,8 +213,8 @@ def right_branch(W, p: str, m: dict, h: torch.Tensor, eps: float, dt=torch.float
 
 
 def parallel_mixer(W, p: str, m: dict, h: torch.Tensor, eps: float, dt=torch.float64) -> torch.Tensor:
-    return (m["left_scale"] * left_branch(W, f"{p}.left", m["left"], h, dt)
-            + m["right_scale"] * right_branch(W, f"{p}.right", m["right"], h, eps, dt))
+    return (m.get("left_scale", 1.0) * left_branch(W, f"{p}.left", m["left"], h, dt)
+            + m.get("right_scale", 1.0) * right_branch(W, f"{p}.right", m["right"], h, eps, dt))
 
 
 def dense_ff(W, p: str, h: torch.Tensor, dt=torch.float64) -> torch.Tensor:
@@ -238,4 +243,4 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dt=torch.float64, tra
             x = x + dense_ff(W, f"{p}.mlp", norm(f"{p}.norm2", x), dt)
         if trace is not None:
             trace.append(x.clone())
-    return (norm("final.norm", x) @ W["embed"].to(dt).t()) * cfg["logit_scale"]
+    return (norm("final.norm", x) @ W["embed"].to(dt).t()) * cfg.get("logit_scale", 1.0)
