@@ -153,13 +153,53 @@ def weights_of(folder: Path) -> Dict[str, torch.Tensor]:
 
 _ORACLE: dict = {}
 
+# The plain model in float32 lies this far (relative to the largest logit) from the plain model in float64 where nothing
+# amplifies rounding; the configurations of this file measure 2e-7 to 9e-7.
+SINGLE_PRECISION_DISTANCE = 5e-7
+# Whole models, relative to the largest logit of the sequence, where nothing amplifies rounding.  float32: only the
+# order of summation differs from the float64 ground truth.  bfloat16: products and activations are rounded to 8 bits of
+# mantissa layer after layer; what a wrong mask, state or page does is told apart by the float32 runs and by the kernel
+# tests with keys that stand out.
+MODEL_TOL = {"float32": 1e-4, "bfloat16": 5e-2}
+
+
+class Truth:
+    """The float64 logits [len, vocab] of one whole sequence from the plain implementation, and for every position how
+    far rounding alone moves it: the distance of the plain model run in float32.  With random weights a position now
+    and then divides by a root mean square of terms that nearly cancel (a head's output before its unit norm), and
+    every rounding before it is magnified there, in any implementation; such a position is allowed that much more."""
+
+    def __init__(self, cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int]):
+        self.logits = P.forward(cfg, W, tokens)
+        self.scale = max(float(self.logits.abs().max()), 1e-6)
+        single = P.forward(cfg, W, tokens, dt=torch.float32).double()
+        self.single = (single - self.logits).abs().amax(-1) / self.scale               # [len]
+
+    def allowed(self, dtype: str) -> torch.Tensor:
+        """[len]: the largest relative distance a position may have in ``dtype``."""
+        if dtype == "float32":
+            return torch.clamp(6 * self.single, min=MODEL_TOL[dtype])
+        return MODEL_TOL[dtype] * torch.clamp(self.single / SINGLE_PRECISION_DISTANCE, min=1.0)
+
+    def excess(self, got: torch.Tensor, rows, dtype: str) -> float:
+        """max over the rows of ``got`` (logits at the positions ``rows``) of distance / allowed distance: below 1
+        passes."""
+        rows = list(rows)
+        got = got.detach().double().cpu().reshape(len(rows), -1)
+        d = (got - self.logits[rows]).abs().amax(-1) / self.scale
+        return float((d / self.allowed(dtype)[rows]).max())
+
+
+def truth(folder: Path, tokens: List[int]) -> Truth:
+    key = (str(folder), tuple(tokens))
+    if key not in _ORACLE:
+        _ORACLE[key] = Truth(raw_config(folder), weights_of(folder), tokens)
+    return _ORACLE[key]
+
 
 def oracle_logits(folder: Path, tokens: List[int]) -> torch.Tensor:
     """float64 logits [len, vocab] of one whole sequence from the plain implementation."""
-    key = (str(folder), tuple(tokens))
-    if key not in _ORACLE:
-        _ORACLE[key] = P.forward(raw_config(folder), weights_of(folder), tokens)
-    return _ORACLE[key]
+    return truth(folder, tokens).logits
 
 
 def plain_greedy(folder: Path, prompt: List[int], n: int) -> List[int]:
