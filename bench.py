@@ -29,7 +29,8 @@ benchmark configuration says; the library's own default of 64 is measured
 beside it (``points.decode_b8_block64``, ``points.prefill_block64_ms``).
 
 ``--compare nizazen`` does the same for the Nizazen design (eight layers that alternate windowed and latent attention,
-dense and routed feed-forwards, on a residual stream of several lanes).  ``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
+dense and routed feed-forwards, on a residual stream of several lanes).  ``--compare revelix`` for the Revelix design (eight layers that alternate retention and attention beside a gated
+recurrence, each with a dense feed-forward).  ``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
 same width, heads, layer runs and feed-forward work per token (random weights, a window as long as Lonasun's chunk):
 prefill and decode throughput of both at a few layer sizes, and for every mixer and feed-forward the device time of
 its kernels against the least time its operations and bytes need at the measured peaks.  It prints one JSON line of
@@ -349,6 +350,48 @@ def nizazen_configs(sz: dict):
     return niza, qwen
 
 
+REVELIX_SIZES = {
+    # width, attention heads, kv heads, head size, window, kept first positions, taps, rotated dimensions of the attention;
+    # heads and head sizes of the gated recurrence beside it; heads and sizes of the retention layers; feed-forward size
+    "w1024": dict(width=1024, heads=8, kv=2, dim=128, window=1024, keep=64, taps=3, rot=64, rec_heads=4, rec_dim=128,
+                  rec_vdim=128, ret_heads=8, ret_dim=128, ret_vdim=128, ff=4096),
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, window=1024, keep=64, taps=3, rot=64, rec_heads=8, rec_dim=128,
+                  rec_vdim=128, ret_heads=16, ret_dim=128, ret_vdim=128, ff=8192),
+    "w2048-d64": dict(width=2048, heads=32, kv=8, dim=64, window=512, keep=16, taps=4, rot=64, rec_heads=16, rec_dim=64,
+                      rec_vdim=64, ret_heads=16, ret_dim=64, ret_vdim=128, ff=6144),
+}
+
+
+def revelix_configs(sz: dict):
+    """(Revelix config dictionary, Qwen2 config dictionary) of equal width and layers: eight Revelix layers that
+    alternate retention and attention beside a gated recurrence, each with a dense feed-forward of two matrices, beside
+    eight dense layers with the attention's heads, head size and window and a feed-forward of three matrices that does
+    the same operations per token."""
+    left = {"conv": sz["taps"], "dim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv"],
+            "mask": {"size": sz["window"], "keep_first": sz["keep"]},
+            "rot": {"base": 1000000.0, "dims": sz["rot"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}},
+            "scale": sz["dim"] ** -0.5, "softcap": 30.0, "vdim": sz["dim"]}
+    right = {"dim": sz["rec_dim"], "heads": sz["rec_heads"], "vdim": sz["rec_vdim"]}
+    par = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+    h = sz["ret_heads"]
+    ret = {"decay": [1.0 - 2.0 ** (-5 - 5 * i / max(h - 1, 1)) for i in range(h)], "dim": sz["ret_dim"], "heads": h,
+           "vdim": sz["ret_vdim"], "rot": {"base": 10000.0, "dims": sz["ret_dim"]}}
+    mlp = {"ff": sz["ff"], "kind": "dense"}
+    reve = {"architecture": "Revelix", "vocab": COMPARE_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [{"type": t, "mixer": m, "mlp": mlp} for t, m in (("retention", ret), ("parallel", par)) * 4]}
+    inter = int(round(sz["ff"] * 2 / 3 / 64)) * 64
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "hidden_size": sz["width"],
+            "intermediate_size": inter, "num_hidden_layers": 8, "num_attention_heads": sz["heads"],
+            "num_key_value_heads": sz["kv"], "head_dim": sz["dim"], "vocab_size": COMPARE_VOCAB, "rms_norm_eps": 1e-5,
+            "rope_theta": 1000000.0, "max_position_embeddings": 8192, "tie_word_embeddings": False,
+            "use_sliding_window": True, "sliding_window": sz["window"], "max_window_layers": 0, "attention_bias": False}
+    return reve, qwen
+
+
+COMPARISONS = {"lonasun": (COMPARE_SIZES, compare_configs), "nizazen": (NIZAZEN_SIZES, nizazen_configs),
+               "revelix": (REVELIX_SIZES, revelix_configs)}
+
+
 def compare_one(cfgd: dict, pk: dict, batch: int, context: int, prompt: int, steps: int, warmup: int, seed: int) -> dict:
     import torch
     from flashdecode_cuda_b200.config import config_from_dict
@@ -457,9 +500,9 @@ def compare_main(args) -> int:
     clocks.start()
     sizes = {}
     design = args.compare
-    table = COMPARE_SIZES if design == "lonasun" else NIZAZEN_SIZES
+    table, configs = COMPARISONS[design]
     for name in (args.compare_sizes.split(",") if args.compare_sizes else table):
-        ours, qwen = compare_configs(table[name]) if design == "lonasun" else nizazen_configs(table[name])
+        ours, qwen = configs(table[name])
         entry = {"sizes": table[name], "dense_intermediate": qwen["intermediate_size"]}
         for key, cfgd in ((design, ours), ("qwen2", qwen)):
             entry[key] = compare_one(cfgd, pk, args.batch, 2048, 2048, min(args.steps, 64), max(3, args.warmup), args.seed)
@@ -688,7 +731,7 @@ def main() -> int:
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the main run through the true 32-bit path (with --no-points)")
-    ap.add_argument("--compare", default="", choices=["", "lonasun", "nizazen"],
+    ap.add_argument("--compare", default="", choices=["", "lonasun", "nizazen", "revelix"],
                     help="measure this design beside the closest dense model at equal sizes instead of the default run")
     ap.add_argument("--compare-sizes", default="", help="with --compare: names of the sizes to run, with commas (default: all)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
