@@ -30,7 +30,7 @@ struct AttnParams {
     int QT, n_splits, split_len, window;
     int chunk;                 // > 0: a query at position i sees key j <= i only if i / chunk == j / chunk
     float scale;
-    // The CUDA-core kernel only (the launchers of the other kernels are not called when any of these is set):
+    // The CUDA-core kernel and the extended prompt kernel only (the launchers of the others are not called when any of these is set):
     float softcap;             // > 0: score <- softcap * tanh(score / softcap) after scaling
     int keep_first;            // with a window: keys at positions below this stay visible however far back they lie
     const float* sink;         // [n_q] or null: exp(sink[h]) is one more term of head h's softmax denominator
@@ -48,6 +48,8 @@ struct AttnParams {
 int launch_attn_decode_mma(const AttnParams& p, int n_rows, cudaStream_t stream);
 // prompt steps (several new tokens per row) on the tensor cores; same return convention
 int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream);
+// prompt steps with capped scores, kept first keys, a keyless softmax term or repeated value heads (head sizes 64 and 128)
+int launch_attn_prefill_mma_ext(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream);
 // the same on the tcgen05 tensor cores (head size 128, block sizes 8..128 that divide 128)
 int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_q_len, cudaStream_t stream);
 

@@ -10,6 +10,12 @@
 // with the online softmax (float, base 2) between the two products, as in the
 // decode kernel.  Tiles start at multiples of 64 in absolute position, so a
 // query's sums do not depend on what else is in the batch.
+//
+// The EXT form of the kernel has the options of the CUDA-core kernel as well: scores capped by a tanh, a window that
+// also keeps the first positions (the key tiles between those and the window's start are not visited), a keyless term
+// per head in the softmax denominator, and weights that are applied to every value head (grid.y = head * v_rep + value
+// head, out [T, n_q, v_rep, D]), written as float on request.  Its weights reach the second product as a sum of two
+// bfloat16 numbers (the rounded weight and what the rounding took away), so they carry 16 bits of mantissa and not 8.
 #include <math.h>
 
 #include "attention.cuh"
@@ -22,14 +28,16 @@ constexpr int PM_THREADS = PM_WARPS * 32;
 constexpr int PM_BM = 64;     // query rows per CTA
 constexpr int PM_BN = 64;     // keys per tile
 
-template <int D>
+template <int D, bool EXT>
 __global__ void __launch_bounds__(PM_THREADS)
 attn_prefill_mma_kernel(const AttnParams p) {
     constexpr int CPR = D / 8;                      // 16-byte chunks per row
     constexpr int TILE_BYTES = PM_BN * D * 2;
     // the last query tiles of a sequence see the most keys: schedule them first, so that the
     // short tiles fill the tail of the launch instead of the long ones
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tile = gridDim.x - 1 - blockIdx.x, b = blockIdx.z;
+    const int h = EXT ? blockIdx.y / p.v_rep : blockIdx.y;                   // query head
+    const int vhi = EXT ? blockIdx.y - h * p.v_rep : 0;
     const int slot = p.row_slot[b];
     if (slot < 0) return;
     const int q_len = p.row_q_len[b];
@@ -38,6 +46,9 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int tok0 = p.row_q_start[b] + tile * PM_BM;
     const int nq = min(PM_BM, q_len - tile * PM_BM);
     const int kvh = h / p.G;
+    const int vh = (EXT && p.v_rep > 1) ? vhi : kvh;                         // the head whose values the weights meet
+    const int keep = (EXT && p.window > 0) ? p.keep_first : 0;               // first positions that stay visible
+    const float softcap = p.softcap;
     const int p_first = ctx + tile * PM_BM;          // position of this CTA's first query
     const int hi = p_first + nq;                      // keys 0 .. last query position
     const int chunk = p.chunk;        // > 0: a query sees the keys of its own chunk of this many positions only
@@ -75,7 +86,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
             const __nv_bfloat16* ksrc = kp;
             const __nv_bfloat16* vsrc = vp;
             int bytes = 0;
-            if (t >= lo && t < hi) {
+            if ((t >= lo || (EXT && t < keep)) && t < hi) {
                 const int col = bs_shift >= 0 ? t >> bs_shift : t / bs;
                 const int in_blk = bs_shift >= 0 ? t & (bs - 1) : t - col * bs;
                 const int blk = p.block_table[(size_t)slot * p.max_blocks + col];
@@ -84,7 +95,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
                 } else {
                     const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
                     ksrc = kp + off;
-                    vsrc = vp + off;
+                    vsrc = EXT ? vp + (((size_t)blk * p.n_kv + vh) * bs + in_blk) * D + cc * 8 : vp + off;
                     bytes = 16;
                 }
             }
@@ -95,8 +106,12 @@ attn_prefill_mma_kernel(const AttnParams p) {
     };
 
     const int t_begin = (lo / PM_BN) * PM_BN;
-    const int n_tiles = (hi - t_begin + PM_BN - 1) / PM_BN;
-    issue(t_begin, 0);                                // this group also carries the queries
+    // tiles of kept first keys that lie wholly before the window's first tile come first; a kept key in a window tile
+    // is loaded and seen there
+    const int n_kf = EXT ? min((min(keep, lo) + PM_BN - 1) / PM_BN, t_begin / PM_BN) : 0;
+    const int n_tiles = n_kf + (hi - t_begin + PM_BN - 1) / PM_BN;
+    auto tile_t0 = [&](int it) { return it < n_kf ? it * PM_BN : t_begin + (it - n_kf) * PM_BN; };
+    issue(tile_t0(0), 0);                             // this group also carries the queries
 
     // head sizes above 128: the query fragments are read from shared memory for every key tile instead of being kept
     // (with the output tile they would not fit the registers)
@@ -116,9 +131,9 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int cs_first = chunk > 0 ? (w_first / chunk) * chunk : 0, cs_last = chunk > 0 ? (w_last / chunk) * chunk : 0;
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int t0 = t_begin + it * PM_BN;
+        const int t0 = tile_t0(it);
         if (it + 1 < n_tiles) {
-            issue(t0 + PM_BN, (it + 1) & 1);
+            issue(tile_t0(it + 1), (it + 1) & 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -133,7 +148,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
         const unsigned char* ks_ = k_s + (it & 1) * TILE_BYTES;
         const unsigned char* vs_ = v_s + (it & 1) * TILE_BYTES;
         // a tile wholly in the future of all rows of this warp contributes nothing
-        const bool skip = t0 > w_last || (p.window > 0 && t0 + PM_BN - 1 < w_first - p.window + 1) ||
+        const bool skip = t0 > w_last || (p.window > 0 && t0 + PM_BN - 1 < w_first - p.window + 1 && !(EXT && t0 < keep)) ||
                           t0 + PM_BN - 1 < cs_first;
         if (!skip) {
             float s[PM_BN / 8][4];
@@ -165,10 +180,12 @@ attn_prefill_mma_kernel(const AttnParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float v = s[nt][e] * scale_log2;
+                    if (EXT && softcap > 0.f) v = softcap * tanhf(s[nt][e] * p.scale / softcap) * 1.4426950408889634f;
                     if (need_mask) {
                         const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = (e >> 1) ? pos_b : pos_a;
-                        const bool ok = t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window) &&
+                        const bool ok = (t >= lo || (EXT && t < keep)) && t < hi && t <= pos &&
+                                        (p.window <= 0 || pos - t < p.window || (EXT && t < keep)) &&
                                         t >= ((e >> 1) ? cs_b : cs_a);
                         if (!ok) v = -INFINITY;
                     }
@@ -206,6 +223,12 @@ attn_prefill_mma_kernel(const AttnParams p) {
                     const uint32_t pa0 = pack_bf16(s[2 * k2][0], s[2 * k2][1]), pa1 = pack_bf16(s[2 * k2][2], s[2 * k2][3]);
                     const uint32_t pa2 = pack_bf16(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
                     const uint32_t pa3 = pack_bf16(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+                    uint32_t pb0 = 0, pb1 = 0, pb2 = 0, pb3 = 0;        // what rounding to bfloat16 took from the weights
+                    if (EXT) {
+                        pb0 = pack_bf16_rest(s[2 * k2][0], s[2 * k2][1]); pb1 = pack_bf16_rest(s[2 * k2][2], s[2 * k2][3]);
+                        pb2 = pack_bf16_rest(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+                        pb3 = pack_bf16_rest(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+                    }
                     const int r = k2 * 16 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
                     for (int np = 0; np < D / 16; ++np) {
@@ -213,6 +236,10 @@ attn_prefill_mma_kernel(const AttnParams p) {
                         ldmatrix_x4_trans(smem_u32(vs_ + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
                         mma_bf16(o[np * 2], pa0, pa1, pa2, pa3, b0, b1);
                         mma_bf16(o[np * 2 + 1], pa0, pa1, pa2, pa3, b2, b3);
+                        if (EXT) {
+                            mma_bf16(o[np * 2], pb0, pb1, pb2, pb3, b0, b1);
+                            mma_bf16(o[np * 2 + 1], pb0, pb1, pb2, pb3, b2, b3);
+                        }
                     }
                 }
             }
@@ -230,8 +257,23 @@ attn_prefill_mma_kernel(const AttnParams p) {
     for (int hh = 0; hh < 2; ++hh) {
         const int r = row_a + hh * 8;
         if (r >= nq) continue;
-        const float inv = l_run[hh] > 0.f ? 1.f / l_run[hh] : 0.f;
-        __nv_bfloat16* orow = og + ((size_t)(tok0 + r) * p.n_q + h) * D + (lane & 3) * 2;
+        float l = l_run[hh], f = 1.f;
+        if (EXT && p.sink != nullptr) {             // one more term in the denominator: exp(sink), no key, no value
+            const float sk = p.sink[h] * 1.4426950408889634f, m = m_run[hh];
+            const float m2 = fmaxf(m, sk);
+            f = m == -INFINITY ? 0.f : exp2f(m - m2);
+            l = l * f + exp2f(sk - m2);
+        }
+        const float inv = l > 0.f ? f / l : 0.f;
+        const size_t orow_i = EXT ? ((size_t)(tok0 + r) * p.n_q + h) * p.v_rep + vhi : (size_t)(tok0 + r) * p.n_q + h;
+        if (EXT && p.out_f32) {
+            float* orow = static_cast<float*>(p.out) + orow_i * D + (lane & 3) * 2;
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<float2*>(orow + nt * 8) = make_float2(o[nt][hh * 2] * inv, o[nt][hh * 2 + 1] * inv);
+            continue;
+        }
+        __nv_bfloat16* orow = og + orow_i * D + (lane & 3) * 2;
 #pragma unroll
         for (int nt = 0; nt < D / 8; ++nt)
             *reinterpret_cast<__nv_bfloat162*>(orow + nt * 8) =
@@ -239,10 +281,10 @@ attn_prefill_mma_kernel(const AttnParams p) {
     }
 }
 
-template <int D>
+template <int D, bool EXT>
 static int launch_pm(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(PM_BM + 4 * PM_BN) * D * 2;
-    auto k = attn_prefill_mma_kernel<D>;
+    auto k = attn_prefill_mma_kernel<D, EXT>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -250,19 +292,29 @@ static int launch_pm(const AttnParams& p, int n_rows, int max_q_len, cudaStream_
         configured = true;
     }
     const int q_tiles = (max_q_len + PM_BM - 1) / PM_BM;
-    if (p.n_q > 65535 || n_rows > 65535) return 1;
-    dim3 grid(q_tiles, p.n_q, n_rows);
+    const int heads = EXT ? p.n_q * p.v_rep : p.n_q;
+    if (heads > 65535 || n_rows > 65535) return 1;
+    dim3 grid(q_tiles, heads, n_rows);
     k<<<grid, PM_THREADS, smem, stream>>>(p);
-    return check_launch("attention_prefill_mma");
+    return check_launch(EXT ? "attention_ext_prefill_mma" : "attention_prefill_mma");
 }
 
 int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
     if (p.n_splits != 1) return 1;
-    if (p.d == 128) return launch_pm<128>(p, n_rows, max_q_len, stream);
-    if (p.d == 64) return launch_pm<64>(p, n_rows, max_q_len, stream);
+    if (p.d == 128) return launch_pm<128, false>(p, n_rows, max_q_len, stream);
+    if (p.d == 64) return launch_pm<64, false>(p, n_rows, max_q_len, stream);
     // wider heads (one cached latent as key and value of many query heads): rows of whole 128-byte swizzle groups
-    if (p.d == 256) return launch_pm<256>(p, n_rows, max_q_len, stream);
-    if (p.d == 192) return launch_pm<192>(p, n_rows, max_q_len, stream);
+    if (p.d == 256) return launch_pm<256, false>(p, n_rows, max_q_len, stream);
+    if (p.d == 192) return launch_pm<192, false>(p, n_rows, max_q_len, stream);
+    return 1;
+}
+
+// The form with the capped scores, kept first keys, keyless term and repeated value heads; returns 1 for sizes it does
+// not take.
+int launch_attn_prefill_mma_ext(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
+    if (p.n_splits != 1 || p.d != p.dv || p.chunk > 0) return 1;
+    if (p.d == 128) return launch_pm<128, true>(p, n_rows, max_q_len, stream);
+    if (p.d == 64) return launch_pm<64, true>(p, n_rows, max_q_len, stream);
     return 1;
 }
 

@@ -441,12 +441,13 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                           int n_splits, int split_len, float* scratch, int* counters, int* status, int use_mma,
                           cudaStream_t stream, const void* prefetch = nullptr, unsigned long long prefetch_bytes = 0,
                           float softcap = 0.f, int keep_first = 0, const float* sink = nullptr, int v_rep = 1,
-                          int out_f32 = 0) {
+                          int out_f32 = 0, int ext_mma = 0) {
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(softcap >= 0.f && keep_first >= 0 && v_rep >= 1 && (v_rep == 1 || v_rep == n_kv), -2,
                "attention: soft cap %g, %d kept first keys, weights applied to %d value heads of %d", softcap, keep_first,
                v_rep, n_kv);
-    if (softcap > 0.f || (keep_first > 0 && window > 0) || sink != nullptr || v_rep > 1 || out_f32) use_mma = 0;
+    const bool ext = softcap > 0.f || (keep_first > 0 && window > 0) || sink != nullptr || v_rep > 1 || out_f32;
+    if (ext) use_mma = 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
     FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= D_MAX, -2, "attention: head size %d must be a multiple of 8 in [8, %d]", d, D_MAX);
@@ -499,6 +500,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
         rc = use_mma == 2 ? 1 : launch_attn_prefill_tcgen05(p, n_rows, T, max_q_len, stream);
         if (rc == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
     }
+    if (ext && ext_mma && dtype == 1 && max_q_len > 1) rc = launch_attn_prefill_mma_ext(p, n_rows, max_q_len, stream);
     if (rc == 1)
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);
@@ -574,7 +576,8 @@ extern "C" int fd_attention_mma_sync(const void* q, const void* k_pool, const vo
                           window, dv, chunk, n_splits, split_len, scratch, counters, status, 2, stream);
 }
 
-// The CUDA-core kernel with its own options: softcap > 0 caps the scaled scores by a tanh; keep_first: with a window, the
+// Attention with more options (on the CUDA cores; prompts in bfloat16 with heads of 64 or 128 on the tensor cores when
+// use_mma is set): softcap > 0 caps the scaled scores by a tanh; keep_first: with a window, the
 // first so many positions stay visible; sink [n_q] (or null): a keyless term exp(sink[h]) in head h's denominator;
 // v_rep == n_kv: every query head's weights are applied to all value heads and out is [T, n_q, n_kv, dv] (scratch for
 // the split form: fd_attn_scratch_floats(T, n_q * n_kv, dv, n_splits)); out_f32: out is float.
@@ -584,11 +587,11 @@ extern "C" int fd_attention_ext(const void* q, const void* k_pool, const void* v
                                 const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                                 int n_splits, int split_len, float* scratch, int* status, float softcap, int keep_first,
-                                const float* sink, int v_rep, int out_f32, cudaStream_t stream) {
+                                const float* sink, int v_rep, int out_f32, int use_mma, cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
                           window, dv, chunk, n_splits, split_len, scratch, nullptr, status, 0, stream, nullptr, 0,
-                          softcap, keep_first, sink, v_rep, out_f32);
+                          softcap, keep_first, sink, v_rep, out_f32, use_mma);
 }
 
 // o [T, n_q, n_kv, dv] float, mix [n_q, n_q] float; out (dtype 0 float32, 1 bfloat16): pointer to the first output

@@ -38,6 +38,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// what rounding to bfloat16 took away from the two numbers, itself rounded to bfloat16: x ~ bf16(x) + bf16(x - bf16(x))
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi) {
+    const float rl = lo - __bfloat162float(__float2bfloat16_rn(lo)), rh = hi - __bfloat162float(__float2bfloat16_rn(hi));
+    __nv_bfloat162 v = __floats2bfloat162_rn(rl, rh);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
 // byte offset of 16-byte chunk `c` of row `r` in a [rows][D] bf16 tile whose
 // chunks are XOR-swizzled by the row, so that ldmatrix reads hit 8 banks groups
 template <int D>

@@ -97,13 +97,13 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
         "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
-        "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, P],
+        "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, I, P],
         "fd_attn_head_mix": [P, P, P, I, I, I, I, I, I, F, P],
         "fd_add_dyn_tanh": [P, I, P, I, P, P, F, P, I, P, I, I, P],
         "fd_quad_exp_act": [P, P, I, P, LL, P],
         "fd_scale_f32": [P, LL, F, P],
         "fd_axpy_f32": [P, P, I, LL, F, I, P],
-        "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, P],
+        "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, I, I, P, LL, P],
         "fd_head_norm_gate": [P, P, P, I, P, I, I, I, I, I, F, F, P],
         "fd_conv_state_update": [P, I, I, P, P, P, P, I, I, I, P],
         "fd_gate_mul": [P, P, I, P, I, I, I, P],
@@ -135,6 +135,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.fd_launch_count.restype = c_ulonglong
     L.fd_launch_count.argtypes = []
     L.fd_attn_scratch_floats.restype = LL
+    L.fd_linear_scan_segment.argtypes = []
+    L.fd_linear_scan_segment.restype = I
+    L.fd_linear_scan_scratch_floats.argtypes = [I, I, I, I, I]
+    L.fd_linear_scan_scratch_floats.restype = LL
     L.fd_sample_scratch_words.argtypes = [I, I]
     L.fd_sample_scratch_words.restype = LL
 
@@ -691,8 +695,9 @@ def attention_ext(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, o
                   window: int = 0, n_splits: int = 1, split_len: int = 0,
                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, chunk: int = 0,
                   softcap: float = 0.0, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
-                  all_value_heads: bool = False) -> None:
-    """Attention on the CUDA cores with the options only that kernel has.  ``softcap`` > 0: the scaled scores
+                  all_value_heads: bool = False, tensor_cores: bool = True) -> None:
+    """Attention with more options, on the CUDA cores; prompt steps in bfloat16 whose key and value heads both have 64
+    or 128 dimensions run on the tensor cores unless ``tensor_cores`` is False.  ``softcap`` > 0: the scaled scores
     become softcap * tanh(score / softcap).  ``keep_first``: with a window, keys at positions below it stay
     visible.  ``sink`` [n_q] float32: exp(sink[h]) is one more term of head h's softmax denominator; it has
     no key and no value.  ``all_value_heads``: every query head's weights are applied to each of the ``n_kv``
@@ -714,7 +719,7 @@ def attention_ext(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, o
         num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
         n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), int(v_dim), int(chunk), n_splits,
         split_len, _ptr(scratch), _ptr(status), float(softcap), int(keep_first), _ptr(sink), v_rep,
-        int(out.dtype == torch.float32 and q.dtype != torch.float32 or all_value_heads), _stream()))
+        int(out.dtype == torch.float32 and q.dtype != torch.float32 or all_value_heads), int(tensor_cores), _stream()))
 
 
 def _col_ptr(t: torch.Tensor, first_col: int) -> int:
@@ -776,13 +781,15 @@ def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: t
                 row_ctx_len: torch.Tensor, n_rows: int, n_heads: int, head_dim: int, v_head_dim: int,
                 write_state: bool, status: torch.Tensor, decay: Optional[torch.Tensor] = None,
                 lower: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
-                sin: Optional[torch.Tensor] = None, rot_dims: int = 0, k_scale: float = 1.0) -> None:
+                sin: Optional[torch.Tensor] = None, rot_dims: int = 0, k_scale: float = 1.0, max_q_len: int = 0,
+                scratch: Optional[torch.Tensor] = None) -> None:
     """The recurrence S_t = diag(a_t) S_(t-1) + b_t v_t^T, o_t = S_t^T q_t per sequence and head over the step's
     tokens, from ``state`` [slots, heads, head_dim, v_head_dim] (float32, updated when ``write_state``) to ``out``
     [T, heads * v_head_dim] (float32).  q, k and v are column ranges of ``proj`` [T, ld].  ``SCAN_DECAY``: a = decay[h],
     b = rotated k times ``k_scale``, q rotated (the first ``rot_dims`` dimensions, i paired with i + rot_dims / 2).
     ``SCAN_GATED``: the k columns hold the gate's pre-activation z; a = lower + (1 - lower) sigmoid(z), b = 1 - a,
-    q = silu of the q columns."""
+    q = silu of the q columns.  With ``scratch`` (float32, ``linear_scan_scratch_floats`` elements) and ``max_q_len`` (the
+    longest portion of the step), portions longer than two segments are cut into segments that run side by side."""
     T = proj.shape[0]
     assert state.dtype == out.dtype == torch.float32 and state.shape[1:] == (n_heads, head_dim, v_head_dim)
     assert out.shape == (T, n_heads * v_head_dim) and proj.is_contiguous()
@@ -798,7 +805,19 @@ def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: t
                                 mode, _ptr(decay), _ptr(lower), _ptr(cos) if rot_dims else None,
                                 _ptr(sin) if rot_dims else None, cos.shape[0] if rot_dims else 0, rot_dims,
                                 float(k_scale), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
-                                n_rows, n_heads, head_dim, v_head_dim, int(write_state), _ptr(status), _stream()))
+                                n_rows, n_heads, head_dim, v_head_dim, int(write_state), _ptr(status), T, int(max_q_len),
+                                _ptr(scratch) if scratch is not None else None,
+                                scratch.numel() if scratch is not None else 0, _stream()))
+
+
+def linear_scan_segment() -> int:
+    """Tokens of a segment of ``linear_scan``; portions longer than two of them run in segments."""
+    return lib().fd_linear_scan_segment()
+
+
+def linear_scan_scratch_floats(T: int, n_rows: int, n_heads: int, head_dim: int, v_head_dim: int) -> int:
+    """float32 elements of scratch memory with which ``linear_scan`` runs a step of T tokens in n_rows sequences in segments."""
+    return int(lib().fd_linear_scan_scratch_floats(T, n_rows, n_heads, head_dim, v_head_dim))
 
 
 def head_norm_gate(o: torch.Tensor, out: torch.Tensor, first_col: int, n_heads: int, v_head_dim: int, eps: float,

@@ -40,6 +40,13 @@ class _StateMixer(Mixer):
     def out_proj(self) -> torch.Tensor:
         return self.w_o
 
+    def scan_scratch(self, ctx) -> Optional[torch.Tensor]:
+        """Scratch memory for a step with a portion long enough to run in segments; None for the others."""
+        if ctx.max_q_len <= 2 * K.linear_scan_segment():
+            return None
+        n = K.linear_scan_scratch_floats(ctx.T, ctx.n_rows, self.n_heads, self.d, self.dv)
+        return ctx.ws.get("scan_segments", (n,), torch.float32)
+
     def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
         T, ws, rt = ctx.T, ctx.ws, self.rt
         proj = ws.get("rec_proj", (T, self.w_in.shape[0]), x.dtype)
@@ -97,7 +104,8 @@ class Retention(_StateMixer):
         K.linear_scan(proj, col0, col0 + nk, col0 + 2 * nk, lc.states["state"], o, K.SCAN_DECAY, ctx.row_slot,
                       ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv,
                       lc.writes, self.rt.status, decay=self.decay_dev, cos=rope.cos if self.rot_dims else None,
-                      sin=rope.sin if self.rot_dims else None, rot_dims=self.rot_dims, k_scale=self.d ** -0.5)
+                      sin=rope.sin if self.rot_dims else None, rot_dims=self.rot_dims, k_scale=self.d ** -0.5,
+                      max_q_len=ctx.max_q_len, scratch=self.scan_scratch(ctx))
         K.head_norm_gate(o, act, act_col, self.n_heads, self.dv, self.eps, None, proj, col0 + 2 * nk + nv, scale)
         return act
 
@@ -146,6 +154,6 @@ class GatedLinearRecurrence(_StateMixer):
         o = ctx.ws.get("scan_out", (ctx.T, nv), torch.float32)
         K.linear_scan(proj, col0, col0 + nk, col0 + 2 * nk, lc.states["state"], o, K.SCAN_GATED, ctx.row_slot,
                       ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv,
-                      lc.writes, self.rt.status, lower=self.lower)
+                      lc.writes, self.rt.status, lower=self.lower, max_q_len=ctx.max_q_len, scratch=self.scan_scratch(ctx))
         K.head_norm_gate(o, act, act_col, self.n_heads, self.dv, self.eps, self.norm_w, None, 0, scale)
         return act

@@ -171,8 +171,9 @@ def test_convolution_interleaved_rotation_and_append(dtype, taps, rot, d, dv, cu
             assert torch.equal(state[slots[r]].cpu(), u[r][n - (taps - 1):, col0:col0 + C].float())
 
 
-def _scan_in_portions(dt, proj_of, cols, mode, H, d, dv, lens, cuts, **kw):
-    """Run ``K.linear_scan`` over two sequences cut into portions; returns (outputs per sequence, final states)."""
+def _scan_in_portions(dt, proj_of, cols, mode, H, d, dv, lens, cuts, segments=False, **kw):
+    """Run ``K.linear_scan`` over two sequences cut into portions; returns (outputs per sequence, final states).
+    ``segments``: with scratch memory, so that portions longer than two segments run as segments side by side."""
     slots = [3, 1]
     state = torch.zeros(5, H, d, dv, device=DEV)
     state[4] = 7.0                                           # a slot nobody uses stays as it is
@@ -187,6 +188,9 @@ def _scan_in_portions(dt, proj_of, cols, mode, H, d, dv, lens, cuts, **kw):
         proj = torch.cat([proj_of[r][done[r]:done[r] + n] for r, n in zip(rows, q_lens)]).to(dt).to(DEV).contiguous()
         _, _, row_slot, q_start, q_len, ctx_len = step_arrays([done[r] for r in rows], q_lens, [slots[r] for r in rows])
         out = torch.full((proj.shape[0], H * dv), float("nan"), device=DEV)
+        if segments:
+            n_scr = K.linear_scan_scratch_floats(proj.shape[0], len(rows), H, d, dv)
+            kw = dict(kw, max_q_len=max(q_lens), scratch=torch.full((n_scr,), float("nan"), device=DEV))
         K.linear_scan(proj, cols[0], cols[1], cols[2], state, out, mode, row_slot, q_start, q_len, ctx_len, len(rows),
                       H, d, dv, True, status, **kw)
         at = 0
@@ -236,6 +240,67 @@ def test_retention_recurrence_in_portions(dtype, H, d, dv, rot):
         assert rel_err(states[r], final) < 2e-5
 
 
+SEGMENT_CASES = [(2, 16, 8, 16), (3, 24, 40, 8), (2, 136, 24, 136), (2, 128, 128, 64), (1, 256, 72, 2)]
+# portions that are many segments, exactly whole segments, one token more and less than that, two segments and one
+# token (the shortest that is cut), and short ones that are not cut, each going on from the state the one before left
+SEGMENT_LENS, SEGMENT_CUTS = [459, 262], [192, 129, 1, 63, 65, 3, 128]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,d,dv,rot", SEGMENT_CASES)
+def test_retention_recurrence_in_segments(dtype, H, d, dv, rot):
+    """Long portions run as segments side by side that are chained afterwards; against the plain token-by-token
+    recurrence over the whole sequences, with two sequences of unequal length in every step."""
+    assert K.linear_scan_segment() == 64
+    torch.manual_seed(H * d + dv + 2)
+    dt = TD[dtype]
+    lens = SEGMENT_LENS
+    nk, nv = H * d, H * dv
+    proj_of = [(torch.randn(n, 2 * nk + nv + 3)).to(dt).float() for n in lens]
+    decay = ([0.97, 1.0, 0.5, 0.999] * H)[:H]
+    pos = RotaryScaled(rot, 1000.0)
+    pos.prepare(512, _Rt)
+    got, states = _scan_in_portions(dt, proj_of, (0, nk, 2 * nk), K.SCAN_DECAY, H, d, dv, lens, SEGMENT_CUTS, segments=True,
+                                    decay=torch.tensor(decay, device=DEV), cos=pos.cos, sin=pos.sin, rot_dims=rot,
+                                    k_scale=d ** -0.5)
+    fr, mag = P.rot_frequencies(rot, 1000.0)
+    for r, n in enumerate(lens):
+        x = proj_of[r].double()
+        q = P.rotate(x[:, :nk].reshape(n, H, d), torch.arange(n), rot, fr, mag, interleaved=False)
+        k = P.rotate(x[:, nk:2 * nk].reshape(n, H, d), torch.arange(n), rot, fr, mag, interleaved=False) * d ** -0.5
+        v = x[:, 2 * nk:2 * nk + nv].reshape(n, H, dv)
+        assert rel_err(got[r], P.decayed_recurrence(q, k, v, decay).reshape(n, nv)) < 2e-5
+        final = torch.zeros(H, d, dv, dtype=torch.float64)
+        for t in range(n):
+            final = torch.tensor(decay).double()[:, None, None] * final + k[t][:, :, None] * v[t][:, None, :]
+        assert rel_err(states[r], final) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,d,dv,rot", SEGMENT_CASES)
+def test_gated_recurrence_in_segments(dtype, H, d, dv, rot):
+    """The same with a forget gate per channel, whose product over a segment is what chains it to the next; lower bounds
+    of 0 and 1 included, and gates near 0, whose products over a segment vanish."""
+    torch.manual_seed(H * d + dv + 3)
+    dt = TD[dtype]
+    lens = SEGMENT_LENS
+    nk, nv = H * d, H * dv
+    proj_of = [(torch.randn(n, 2 * nk + nv) * 2).to(dt).float() for n in lens]
+    for x in proj_of:
+        x[:, nk + 1] -= 12.0                                 # a channel whose gate stays near its lower bound of 0
+    lower = torch.rand(nk)
+    lower[0], lower[1], lower[-1] = 0.0, 0.0, 1.0
+    got, states = _scan_in_portions(dt, proj_of, (0, nk, 2 * nk), K.SCAN_GATED, H, d, dv, lens, SEGMENT_CUTS, segments=True,
+                                    lower=lower.to(DEV))
+    for r, n in enumerate(lens):
+        x = proj_of[r].double()
+        q = F.silu(x[:, :nk]).reshape(n, H, d)
+        f = (lower.double() + (1 - lower.double()) * torch.sigmoid(x[:, nk:2 * nk])).reshape(n, H, d)
+        v = x[:, 2 * nk:].reshape(n, H, dv)
+        assert rel_err(got[r], P.gated_recurrence(q, f, v).reshape(n, nv)) < 2e-5
+    assert bool((states[0][-1, -1] == 0).all())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,d,dv,rot", SCAN_CASES)
 def test_gated_recurrence_in_portions(dtype, H, d, dv, rot):
@@ -281,7 +346,7 @@ def test_norm_per_head_with_gate_into_a_shared_buffer(dtype, H, dv, weighted, ga
     assert bool((out[:, :col] == 9.0).all()) and bool((out[:, col + H * dv:] == 9.0).all())
 
 
-def _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, softcap, bs, S, portions, seed, far=False):
+def _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, softcap, bs, S, portions, seed, far=False, tensor_cores=True):
     """Keys that stand out: every seventh position (each is the oldest key inside the window of one query and the
     newest outside it for the next), the last kept position and the first that is not kept, and - with ``far`` - one
     key hundreds of positions back that only the kept range or a long window still shows.  A visibility that is one
@@ -331,7 +396,7 @@ def _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, softcap, bs, S, p
         K.attention_ext(q[at:at + n].reshape(n, n_q * d).to(DEV).contiguous(), k_pool, v_pool, per_head, table, tok_row,
                         row_slot, q_start, q_len, ctx_len, 1, n, n_q, n_kv, d, scale, window or 0, n_splits, split_len,
                         scratch, status, softcap=softcap or 0.0, keep_first=keep if window else 0, sink=sink.to(DEV),
-                        all_value_heads=True)
+                        all_value_heads=True, tensor_cores=tensor_cores)
         out = torch.full((n, 2 + n_q * dv), 5.0, dtype=dt, device=DEV)
         K.attn_head_mix(per_head, talk.to(DEV), out, 2, n_q, n_kv, dv, 1.0)
         assert bool((out[:, :2] == 5.0).all())
@@ -351,14 +416,19 @@ MIX_CASES = [  # d, dv, G, n_kv, window, kept, soft cap, block size, length
     (24, 40, 2, 2, None, 0, 2.0, 16, 90),      # no window: every earlier key
     (128, 128, 2, 1, 1, 1, 5.0, 32, 80),       # a window of the query itself, plus the very first key
     (8, 8, 2, 2, 40, 3, 20.0, 16, 330),        # keys far back: the kept ones stay visible 300 positions on
+    (64, 64, 2, 2, 70, 5, 15.0, 16, 400),      # tiles of keys between the kept ones and the window that nobody sees
+    (128, 128, 2, 2, 100, 70, 10.0, 64, 450),  # kept positions that fill more than one tile of keys
+    (64, 64, 4, 2, 200, 130, None, 8, 500),    # kept positions that end inside the tile where a window starts
 ]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", MIX_CASES)
-def test_capped_windowed_attention_with_sink_and_mixed_heads_whole_prompt(dtype, case):
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_capped_windowed_attention_with_sink_and_mixed_heads_whole_prompt(dtype, case, tensor_cores):
+    """With and without the tensor-core form of the kernel, which takes bfloat16 prompts with heads of 64 and 128."""
     d, dv, G, n_kv, window, keep, cap, bs, S = case
-    _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, cap, bs, S, [S], seed=1, far=True)
+    _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, cap, bs, S, [S], seed=1, far=True, tensor_cores=tensor_cores)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
