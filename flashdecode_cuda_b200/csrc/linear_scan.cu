@@ -12,12 +12,14 @@
 // Everything after the projection is float: angles' use, gates, decay, state, output.
 //
 // A CTA of 128 threads takes one sequence of the step, one head and a tile of value columns.  DS = 4 (d <= 128) or 8
-// adjacent lanes share a column and hold every DS-th row of it in registers (at most 32 each); the tokens' q, a, b
-// and v are staged in shared memory a chunk at a time by all threads, then the chunk is walked token by token:
-// per token a thread does two fused multiply-adds per state element it holds and the DS lanes add their partial
-// outputs with shuffles.
+// adjacent lanes share a column and each holds 8, 16 or 32 adjacent rows of it in registers (rows beyond d are
+// padding whose q, a and b are zero); the tokens' q, a, b and v are staged in shared memory a chunk at a time by all
+// threads, then the chunk is walked token by token: per token a thread reads its rows' q, a and b four at a time, does
+// two fused multiply-adds per state element it holds, and the DS lanes add their partial outputs with shuffles.
 //
-// Long portions (prompts) are cut into segments of `seg_len` tokens that run side by side, in three launches:
+// Long portions (prompts) are cut into segments of `seg_len` tokens that run side by side.  A first launch leaves every
+// token's q, a, b and v as floats in the order the recurrence reads them (its CTAs then copy them to shared memory
+// with cp.async, a chunk ahead of the one they walk); then three launches:
 //  1. every segment but a sequence's last walks its tokens from a zero state and leaves U = its own contribution to
 //     the state [d, dv] and, with a forget gate, the product A of its gates per channel (a constant decay's product is
 //     decay^seg_len);
@@ -31,6 +33,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace fd {
 
@@ -53,17 +56,114 @@ struct ScanParams {
     // from its chained start state, writes outputs.  seg_state [segment slots, H, d, dv], seg_decay [segment slots, H, d].
     int phase, seg_len, n_seg;
     float* seg_state; float* seg_decay;
+    float* prep; float* prep_v; int dvp;      // the preparing kernel's q, b (and a) [T, H, NA * CS] and v [T, H, dvp]
 };
 
 // Segment s of step row r has the slot q_start / seg_len + r + s: slots of different rows never meet, and a step of T
 // tokens and n rows needs at most T / seg_len + n + 1 of them.
 __device__ __forceinline__ int seg_slot(int q_start, int seg_len, int r, int s) { return q_start / seg_len + r + s; }
 
-template <typename T, int PHASE>
+// Shared-memory place of channel i of a token: a thread's NR rows are adjacent (read four at a time), and the DS groups
+// of rows are NR + 4 floats apart so that the DS lanes of a column read different banks.
+template <int NR> __device__ __forceinline__ int chan_at(int i) { return (i / NR) * (NR + 4) + (i % NR); }
+
+// q, b (and a) of n tokens from `tok0` on (the first at position pos0), as floats: token tt's q goes to
+// dst + tt * tok_stride + chan_at(i), its b CS floats further and its a 2 CS floats further.  A thread's loads of several
+// elements are all issued before the first of them is used.
+template <typename T, int NR>
+__device__ __forceinline__ void stage_tokens(const ScanParams& p, int h, int tok0, int pos0, int n, float* dst,
+                                             size_t tok_stride, int DP, int CS, int tid, int n_threads, bool report) {
+    const T* proj = static_cast<const T*>(p.proj);
+    const int d = p.d, half = p.rot >> 1;
+    constexpr int UNR = 4;
+    for (int idx0 = tid; idx0 < n * DP; idx0 += n_threads * UNR) {
+        float xq[UNR], xk[UNR], yq[UNR], yk[UNR], cc[UNR], ss[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int idx = idx0 + u * n_threads;
+            xq[u] = xk[u] = yq[u] = yk[u] = ss[u] = 0.f; cc[u] = 1.f;
+            if (idx >= n * DP) continue;
+            const int tt = idx / DP, i = idx - tt * DP;
+            if (i >= d) continue;
+            const size_t row = (size_t)(tok0 + tt) * p.ld;
+            xq[u] = to_float(proj[row + p.q_col + h * d + i]);
+            xk[u] = to_float(proj[row + p.k_col + h * d + i]);
+            if (p.mode == 0 && i < p.rot) {
+                const int pos = pos0 + tt;
+                if (pos < p.table_len) {
+                    const bool first = i < half;
+                    const int pi = first ? i : i - half;
+                    const int partner = first ? i + half : i - half;
+                    cc[u] = p.cos_t[(size_t)pos * half + pi];
+                    ss[u] = first ? -p.sin_t[(size_t)pos * half + pi] : p.sin_t[(size_t)pos * half + pi];
+                    yq[u] = to_float(proj[row + p.q_col + h * d + partner]);
+                    yk[u] = to_float(proj[row + p.k_col + h * d + partner]);
+                } else if (i == 0 && report) {
+                    set_status(p.status, STATUS_BAD_POSITION);
+                }
+            } else if (p.mode == 1) {
+                cc[u] = p.lower[h * d + i];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int idx = idx0 + u * n_threads;
+            if (idx >= n * DP) continue;
+            const int tt = idx / DP, i = idx - tt * DP;
+            float* at = dst + tt * tok_stride + chan_at<NR>(i);
+            if (i >= d) {
+                at[0] = 0.f; at[CS] = 0.f;
+                if (p.mode == 1) at[2 * CS] = 0.f;
+            } else if (p.mode == 0) {
+                at[0] = xq[u] * cc[u] + yq[u] * ss[u];              // first half: x c - y s; second half: x c + y s
+                at[CS] = (xk[u] * cc[u] + yk[u] * ss[u]) * p.k_scale;
+            } else {
+                const float lo = cc[u];
+                const float f = lo + (1.f - lo) / (1.f + expf(-xk[u]));
+                at[0] = xq[u] / (1.f + expf(-xq[u]));
+                at[CS] = 1.f - f;
+                at[2 * CS] = f;
+            }
+        }
+    }
+}
+
+constexpr int PREP_TOKENS = 16;        // tokens a CTA of the preparing kernel takes
+constexpr int PREP_THREADS = 256;
+
+// Before a step's segments run: q, b (and a) and v of every token as floats in the layout the recurrence reads them
+// in, prep [T, H, NA * CS] and prep_v [T, H, dvp], so that its CTAs (several per head, twice over) copy them instead of
+// each working them out.  blockIdx.x = (row * segments + segment) * (seg_len / PREP_TOKENS) + part.
+template <typename T, int NR>
+__global__ void __launch_bounds__(PREP_THREADS)
+scan_prepare_kernel(const ScanParams p) {
+    const int parts = p.seg_len / PREP_TOKENS;
+    const int rs = blockIdx.x / parts, part = blockIdx.x - rs * parts;
+    const int r = rs / p.n_seg, seg = rs - r * p.n_seg, h = blockIdx.y;
+    if (p.row_slot[r] < 0) return;
+    const int q_start = p.row_q_start[r], q_len = p.row_q_len[r], ctx = p.row_ctx_len[r];
+    const int t0 = seg * p.seg_len + part * PREP_TOKENS;
+    if (t0 >= q_len) return;
+    const int n = min(PREP_TOKENS, q_len - t0);
+    const int DP = p.DS * NR, CS = p.DS * (NR + 4);
+    const size_t TS = (size_t)(p.mode ? 3 : 2) * CS;
+    stage_tokens<T, NR>(p, h, q_start + t0, ctx + t0, n, p.prep + ((size_t)(q_start + t0) * p.H + h) * TS, p.H * TS, DP, CS,
+                        threadIdx.x, PREP_THREADS, h == 0);
+    const T* proj = static_cast<const T*>(p.proj);
+    for (int idx = threadIdx.x; idx < n * p.dvp; idx += PREP_THREADS) {
+        const int tt = idx / p.dvp, c = idx - tt * p.dvp;
+        const size_t tok = q_start + t0 + tt;
+        p.prep_v[(tok * p.H + h) * p.dvp + c] = c < p.dv ? to_float(proj[tok * p.ld + p.v_col + h * p.dv + c]) : 0.f;
+    }
+}
+
+template <typename T, int PHASE, int NR>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(const ScanParams p) {
     // blockIdx.x = (row * segments + segment) * tiles + tile of value columns
-    const int tiles = (p.dv + SCAN_THREADS / p.DS - 1) / (SCAN_THREADS / p.DS);
+    const int DS = p.DS, TC = p.TC;
+    const int VT = SCAN_THREADS / DS;
+    const int tiles = (p.dv + VT - 1) / VT;
     const int rs = blockIdx.x / tiles, tile = blockIdx.x - rs * tiles;
     const int r = rs / p.n_seg, seg = rs - r * p.n_seg, h = blockIdx.y;
     const int slot = p.row_slot[r];
@@ -75,115 +175,116 @@ linear_scan_kernel(const ScanParams p) {
     const bool last_seg = t_end == q_len;
     if (PHASE == 1 && last_seg) return;              // nothing follows a sequence's last segment
     const int sslot = PHASE == 0 ? 0 : seg_slot(q_start, p.seg_len, r, seg);
-    const int d = p.d, dv = p.dv, DS = p.DS, TC = p.TC;
-    const int VT = SCAN_THREADS / DS;
+    const int d = p.d, dv = p.dv;
+    const int DP = DS * NR;                          // channels with the padding (their q, a and b are zero)
+    const int CS = DS * (NR + 4);                    // floats of one of a token's q, b and a in shared memory
+    const int TS = (p.mode ? 3 : 2) * CS;            // floats of a token's q, b (and a)
+    const int BUF = TC * (TS + VT);                  // floats of a chunk: [TC][TS], then v [TC][VT]
     const int tid = threadIdx.x;
     const int vl = tid / DS, ds = tid - vl * DS;
     const int v = tile * VT + vl;
     const bool v_ok = v < dv;
 
-    extern __shared__ float sm[];
-    float* q_s = sm;                    // [TC][d]
-    float* b_s = q_s + TC * d;          // [TC][d]
-    float* a_s = b_s + TC * d;          // [TC][d] (mode 1)
-    float* v_s = a_s + (p.mode ? TC * d : 0);   // [TC][VT]
+    extern __shared__ __align__(16) float sm[];     // one chunk (PHASE 0) or two, filled in turn
 
-    const T* proj = static_cast<const T*>(p.proj);
     float* st = p.state + ((size_t)slot * p.H + h) * d * dv;
     // a segment after the first starts from what the chaining left in the slot of the segment before it
     const float* st_in = (PHASE == 3 && seg > 0) ? p.seg_state + ((size_t)(sslot - 1) * p.H + h) * d * dv : st;
-    float S[SCAN_RPT];
-    float A[PHASE == 1 ? SCAN_RPT : 1];
+    float S[NR];                        // rows ds * NR .. ds * NR + NR - 1 of column v
+    float A[PHASE == 1 ? NR : 1];
 #pragma unroll
-    for (int ii = 0; ii < SCAN_RPT; ++ii) {
-        const int i = ii * DS + ds;
+    for (int ii = 0; ii < NR; ++ii) {
+        const int i = ds * NR + ii;
         S[ii] = (PHASE != 1 && i < d && v_ok) ? st_in[(size_t)i * dv + v] : 0.f;
         if (PHASE == 1) A[ii] = 1.f;
     }
     const float g = p.mode == 0 ? p.decay[h] : 0.f;
-    const int half = p.rot >> 1;
+    const int my = ds * (NR + 4);
 
-    for (int c0 = t_begin; c0 < t_end; c0 += TC) {
+    // segments copy what the preparing kernel left, a chunk ahead of the one that is walked
+    auto issue = [&](int c0, int buf) {
         const int n = min(TC, t_end - c0);
-        __syncthreads();
-        for (int idx = tid; idx < n * d; idx += SCAN_THREADS) {
-            const int tt = idx / d, i = idx - tt * d;
-            const size_t row = (size_t)(q_start + c0 + tt) * p.ld;
-            const float xq = to_float(proj[row + p.q_col + h * d + i]);
-            const float xk = to_float(proj[row + p.k_col + h * d + i]);
-            if (p.mode == 0) {
-                float qv = xq, kv = xk;
-                if (i < p.rot) {
-                    const int pos = ctx + c0 + tt;
-                    if (pos < p.table_len) {
-                        const bool first = i < half;
-                        const int pi = first ? i : i - half;
-                        const int partner = first ? i + half : i - half;
-                        const float c = p.cos_t[(size_t)pos * half + pi], s = p.sin_t[(size_t)pos * half + pi];
-                        const float yq = to_float(proj[row + p.q_col + h * d + partner]);
-                        const float yk = to_float(proj[row + p.k_col + h * d + partner]);
-                        qv = first ? xq * c - yq * s : xq * c + yq * s;
-                        kv = first ? xk * c - yk * s : xk * c + yk * s;
-                    } else if (i == 0 && h == 0 && tile == 0) {
-                        set_status(p.status, STATUS_BAD_POSITION);
-                    }
-                }
-                q_s[idx] = qv;
-                b_s[idx] = kv * p.k_scale;
-            } else {
-                const float lo = p.lower[h * d + i];
-                const float f = lo + (1.f - lo) / (1.f + expf(-xk));
-                q_s[idx] = xq / (1.f + expf(-xq));
-                a_s[idx] = f;
-                b_s[idx] = 1.f - f;
+        float* dst = sm + buf * BUF;
+        const int cpt = TS >> 2, cpv = VT >> 2;      // 16-byte pieces per token
+        for (int idx = tid; idx < n * cpt; idx += SCAN_THREADS) {
+            const int tt = idx / cpt, c = idx - tt * cpt;
+            cp_async16(smem_u32(dst + tt * TS + c * 4), p.prep + ((size_t)(q_start + c0 + tt) * p.H + h) * TS + c * 4, 16);
+        }
+        for (int idx = tid; idx < n * cpv; idx += SCAN_THREADS) {
+            const int tt = idx / cpv, c = idx - tt * cpv;
+            const int col = tile * VT + c * 4;
+            const bool in = col < p.dvp;
+            cp_async16(smem_u32(dst + TC * TS + tt * VT + c * 4),
+                       in ? p.prep_v + ((size_t)(q_start + c0 + tt) * p.H + h) * p.dvp + col : p.prep_v, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    if (PHASE != 0) issue(t_begin, 0);
+
+    int it = 0;
+    for (int c0 = t_begin; c0 < t_end; c0 += TC, ++it) {
+        const int n = min(TC, t_end - c0);
+        float* buf = sm;
+        if (PHASE == 0) {
+            __syncthreads();
+            stage_tokens<T, NR>(p, h, q_start + c0, ctx + c0, n, sm, TS, DP, CS, tid, SCAN_THREADS, h == 0 && tile == 0);
+            const T* proj = static_cast<const T*>(p.proj);
+            for (int idx = tid; idx < n * VT; idx += SCAN_THREADS) {
+                const int tt = idx / VT, c = idx - tt * VT;
+                const int vc = tile * VT + c;
+                sm[TC * TS + idx] = vc < dv ? to_float(proj[(size_t)(q_start + c0 + tt) * p.ld + p.v_col + h * dv + vc]) : 0.f;
             }
+            __syncthreads();
+        } else {
+            if (c0 + TC < t_end) {
+                issue(c0 + TC, (it + 1) & 1);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            buf = sm + (it & 1) * BUF;
         }
-        for (int idx = tid; idx < n * VT; idx += SCAN_THREADS) {
-            const int tt = idx / VT, c = idx - tt * VT;
-            const int vc = tile * VT + c;
-            v_s[idx] = vc < dv ? to_float(proj[(size_t)(q_start + c0 + tt) * p.ld + p.v_col + h * dv + vc]) : 0.f;
-        }
-        __syncthreads();
+        const float* v_s = buf + TC * TS;
         for (int tt = 0; tt < n; ++tt) {
             const float vv = v_s[tt * VT + vl];
-            const float* qr = q_s + tt * d;
-            const float* br = b_s + tt * d;
-            const float* ar = a_s + tt * d;
-            float o = 0.f;
-            if (p.mode == 0) {
+            const float4* qr = reinterpret_cast<const float4*>(buf + tt * TS + my);
+            const float4* br = reinterpret_cast<const float4*>(buf + tt * TS + CS + my);
+            const float4* ar = reinterpret_cast<const float4*>(buf + tt * TS + 2 * CS + my);
+            float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int ii = 0; ii < SCAN_RPT; ++ii) {
-                    if (ii * DS >= d) break;
-                    const int i = ii * DS + ds;
-                    if (i < d) {
-                        S[ii] = fmaf(g, S[ii], br[i] * vv);
-                        if (PHASE != 1) o = fmaf(S[ii], qr[i], o);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int ii = 0; ii < SCAN_RPT; ++ii) {
-                    if (ii * DS >= d) break;
-                    const int i = ii * DS + ds;
-                    if (i < d) {
-                        S[ii] = fmaf(ar[i], S[ii], br[i] * vv);
-                        if (PHASE == 1) A[ii] *= ar[i];
-                        else o = fmaf(S[ii], qr[i], o);
-                    }
+            for (int j = 0; j < NR / 4; ++j) {
+                const float4 b4 = br[j];
+                float4 a4 = make_float4(g, g, g, g), q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.mode == 1) a4 = ar[j];
+                if (PHASE != 1) q4 = qr[j];
+                S[4 * j + 0] = fmaf(a4.x, S[4 * j + 0], b4.x * vv);
+                S[4 * j + 1] = fmaf(a4.y, S[4 * j + 1], b4.y * vv);
+                S[4 * j + 2] = fmaf(a4.z, S[4 * j + 2], b4.z * vv);
+                S[4 * j + 3] = fmaf(a4.w, S[4 * j + 3], b4.w * vv);
+                if (PHASE == 1) {
+                    if (p.mode == 1) { A[4 * j + 0] *= a4.x; A[4 * j + 1] *= a4.y; A[4 * j + 2] *= a4.z; A[4 * j + 3] *= a4.w; }
+                } else {
+                    o4[0] = fmaf(S[4 * j + 0], q4.x, o4[0]);
+                    o4[1] = fmaf(S[4 * j + 1], q4.y, o4[1]);
+                    o4[2] = fmaf(S[4 * j + 2], q4.z, o4[2]);
+                    o4[3] = fmaf(S[4 * j + 3], q4.w, o4[3]);
                 }
             }
             if (PHASE != 1) {
+                float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
                 for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
                 if (ds == 0 && v_ok) p.out[(size_t)(q_start + c0 + tt) * p.H * dv + h * dv + v] = o;
             }
         }
+        if (PHASE != 0) __syncthreads();             // the chunk is through before its place is filled again
     }
     if (PHASE == 1) {
         float* u = p.seg_state + ((size_t)sslot * p.H + h) * d * dv;
         float* a = p.seg_decay + ((size_t)sslot * p.H + h) * d;
 #pragma unroll
-        for (int ii = 0; ii < SCAN_RPT; ++ii) {
-            const int i = ii * DS + ds;
+        for (int ii = 0; ii < NR; ++ii) {
+            const int i = ds * NR + ii;
             if (i < d && v_ok) u[(size_t)i * dv + v] = S[ii];
             if (i < d && p.mode == 1 && tile == 0 && vl == 0) a[i] = A[ii];
         }
@@ -191,8 +292,8 @@ linear_scan_kernel(const ScanParams p) {
     }
     if (p.write_state && v_ok && last_seg) {
 #pragma unroll
-        for (int ii = 0; ii < SCAN_RPT; ++ii) {
-            const int i = ii * DS + ds;
+        for (int ii = 0; ii < NR; ++ii) {
+            const int i = ds * NR + ii;
             if (i < d) st[(size_t)i * dv + v] = S[ii];
         }
     }
@@ -258,31 +359,56 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int SCAN_SEG = 64;           // tokens of a segment
 
-template <typename T>
-static int scan_launches(const ScanParams& base, int n_rows, int VT, size_t smem, cudaStream_t stream) {
+template <typename T, int NR>
+static int scan_launches(const ScanParams& base, int n_rows, cudaStream_t stream) {
     ScanParams p = base;
+    const int VT = SCAN_THREADS / p.DS;
     const dim3 block(SCAN_THREADS), one(1, 1, 1);
     const unsigned tiles = (p.dv + VT - 1) / VT;
     if (p.n_seg <= 1) {
         p.phase = 0; p.n_seg = 1;
-        return launch("linear_scan", linear_scan_kernel<T, 0>, dim3(tiles * n_rows, p.H, 1), block, smem, stream, one, p);
+        const size_t smem = (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * (NR + 4) + VT) * sizeof(float);
+        return launch("linear_scan", linear_scan_kernel<T, 0, NR>, dim3(tiles * n_rows, p.H, 1), block, smem, stream, one, p);
     }
+    p.TC = p.d <= 128 ? 8 : 4;             // two chunks in shared memory, one of them in flight
+    const size_t smem = 2 * (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * (NR + 4) + VT) * sizeof(float);
+    int rc = launch("linear_scan_prepare", scan_prepare_kernel<T, NR>,
+                    dim3(n_rows * p.n_seg * (p.seg_len / PREP_TOKENS), p.H, 1), dim3(PREP_THREADS), 0, stream, one, p);
+    if (rc) return rc;
     const dim3 grid(tiles * n_rows * p.n_seg, p.H, 1);
     p.phase = 1;
-    int rc = launch("linear_scan_local", linear_scan_kernel<T, 1>, grid, block, smem, stream, one, p);
+    rc = launch("linear_scan_local", linear_scan_kernel<T, 1, NR>, grid, block, smem, stream, one, p);
     if (rc) return rc;
     rc = launch("linear_scan_chain", scan_chain_kernel, dim3((p.d * p.dv + 255) / 256, p.H, n_rows), dim3(256), 0, stream,
                 one, p);
     if (rc) return rc;
     p.phase = 3;
-    return launch("linear_scan", linear_scan_kernel<T, 3>, grid, block, smem, stream, one, p);
+    return launch("linear_scan", linear_scan_kernel<T, 3, NR>, grid, block, smem, stream, one, p);
+}
+
+static int scan_ds(int d) { return d <= 4 * SCAN_RPT ? 4 : 8; }
+static int scan_nr(int d) {
+    const int rows = (d + scan_ds(d) - 1) / scan_ds(d);        // state rows a thread holds
+    return rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+}
+
+template <typename T>
+static int scan_by_rows(const ScanParams& p, int n_rows, cudaStream_t stream) {
+    const int nr = scan_nr(p.d);
+    if (nr == 8) return scan_launches<T, 8>(p, n_rows, stream);
+    if (nr == 16) return scan_launches<T, 16>(p, n_rows, stream);
+    return scan_launches<T, 32>(p, n_rows, stream);
 }
 
 // Tokens of a segment, and the floats of scratch memory that a step of T tokens in n_rows sequences needs to run its
-// recurrences in segments (states and gate products of T / segment + n_rows + 1 segment slots).
+// recurrences in segments: the prepared q, b, a (three places of DS * (NR + 4) floats per token and head) and v, then
+// states and gate products of T / segment + n_rows + 1 segment slots.
 extern "C" int fd_linear_scan_segment() { return SCAN_SEG; }
+static long long scan_prep_floats(int T, int H, int d, int dv) {
+    return (long long)T * H * (3 * scan_ds(d) * (scan_nr(d) + 4) + (dv + 3) / 4 * 4);
+}
 extern "C" long long fd_linear_scan_scratch_floats(int T, int n_rows, int H, int d, int dv) {
-    return (long long)(T / SCAN_SEG + n_rows + 1) * H * ((long long)d * dv + d);
+    return scan_prep_floats(T, H, d, dv) + (long long)(T / SCAN_SEG + n_rows + 1) * H * ((long long)d * dv + d);
 }
 
 // proj [T, ld] of `dtype` (0 float32, 1 bfloat16) holds q at q_col, k (mode 0) or the gate's pre-activation (mode 1)
@@ -310,23 +436,25 @@ extern "C" int fd_linear_scan(const void* proj, int ld, int dtype, int q_col, in
     p.rot = mode == 0 ? rot : 0; p.k_scale = k_scale;
     p.row_slot = row_slot; p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len;
     p.H = H; p.d = d; p.dv = dv; p.mode = mode; p.write_state = write_state; p.status = status;
-    p.DS = d <= 4 * SCAN_RPT ? 4 : 8;
+    p.DS = scan_ds(d);
     p.TC = d <= 128 ? 16 : 8;
     p.phase = 0; p.seg_len = SCAN_SEG; p.n_seg = 1; p.seg_state = nullptr; p.seg_decay = nullptr;
+    p.prep = nullptr; p.prep_v = nullptr; p.dvp = (dv + 3) / 4 * 4;
     if (scratch != nullptr && max_q_len > 2 * SCAN_SEG) {
         const long long slots = T / SCAN_SEG + n_rows + 1;
         FD_REQUIRE(scratch_floats >= fd_linear_scan_scratch_floats(T, n_rows, H, d, dv), -2,
                    "linear_scan: %lld floats of scratch memory for %d tokens in %d sequences", scratch_floats, T, n_rows);
         p.n_seg = (max_q_len + SCAN_SEG - 1) / SCAN_SEG;
-        p.seg_state = scratch;
-        p.seg_decay = scratch + slots * H * d * dv;
+        FD_REQUIRE((uintptr_t)scratch % 16 == 0, -2, "linear_scan: scratch memory must be 16-byte aligned");
+        p.prep = scratch;
+        p.prep_v = scratch + (long long)T * H * (mode ? 3 : 2) * p.DS * (scan_nr(d) + 4);
+        p.seg_state = scratch + scan_prep_floats(T, H, d, dv);
+        p.seg_decay = p.seg_state + slots * H * d * dv;
     }
     FD_REQUIRE(n_rows <= 65535 && (long long)n_rows * p.n_seg * ((dv + 15) / 16) < (1ll << 31), -2,
                "linear_scan: %d rows of %d segments", n_rows, p.n_seg);
-    const int VT = SCAN_THREADS / p.DS;
-    const size_t smem = (size_t)((mode ? 3 : 2) * p.TC * d + p.TC * VT) * sizeof(float);
-    if (dtype == 0) return scan_launches<float>(p, n_rows, VT, smem, stream);
-    return scan_launches<bf16>(p, n_rows, VT, smem, stream);
+    if (dtype == 0) return scan_by_rows<float>(p, n_rows, stream);
+    return scan_by_rows<bf16>(p, n_rows, stream);
 }
 
 // o [T, H * dv] float; w [dv] float or null; gate: pointer to the first gate column of a packed projection with row
