@@ -36,6 +36,7 @@ struct AttnParams {
     const float* sink;         // [n_q] or null: exp(sink[h]) is one more term of head h's softmax denominator
     int v_rep;                 // > 1: every query head's weights are applied to each of v_rep value heads (the pool's
                                // n_kv heads); out is then [T, n_q, v_rep, dv]
+    int v_all;                 // set by the CUDA-core launcher: a CTA takes a key head and all v_rep value heads, not one
     int out_f32;               // out is float whatever the type of q and the pools
     // decode steps on the tensor cores only: memory that a later kernel streams (the next part's first weights), or
     // null; every CTA asks L2 for its share once its own keys and values are through

@@ -123,6 +123,9 @@ attn_prefill_mma_kernel(const AttnParams p) {
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
     const float scale_log2 = p.scale * 1.4426950408889634f;
+    // capped scores: exponent 2 x log2(e) of the score's x = s * scale / cap, and the cap in base-2 units
+    const float cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * p.scale / softcap : 0.f;
+    const float cap_out = softcap * 1.4426950408889634f;
     const int row_a = warp * 16 + (lane >> 2);        // this thread's rows: row_a and row_a + 8
     const int pos_a = p_first + row_a, pos_b = pos_a + 8;
     const int w_first = p_first + warp * 16, w_last = w_first + 15;     // positions of the warp's rows
@@ -180,7 +183,11 @@ attn_prefill_mma_kernel(const AttnParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float v = s[nt][e] * scale_log2;
-                    if (EXT && softcap > 0.f) v = softcap * tanhf(s[nt][e] * p.scale / softcap) * 1.4426950408889634f;
+                    if (EXT && softcap > 0.f) {
+                        // cap * tanh(x) as cap * (1 - 2 / (e^(2x) + 1)), in float: its error stays below 1e-7 of the cap
+                        const float ex = exp2f(s[nt][e] * cap_in);
+                        v = fmaf(-2.f * cap_out, __fdividef(1.f, ex + 1.f), cap_out);
+                    }
                     if (need_mask) {
                         const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = (e >> 1) ? pos_b : pos_a;

@@ -67,7 +67,10 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_tile_kernel(const AttnParams p) {
     const int b = blockIdx.z;
-    const int kvh = blockIdx.y / p.v_rep, vh = p.v_rep > 1 ? blockIdx.y - kvh * p.v_rep : kvh;     // key head, value head
+    // key head and value head; with v_all the CTA applies its weights to all v_rep value heads in turn (VR of them)
+    const int VR = p.v_all ? p.v_rep : 1;
+    const int kvh = p.v_all ? blockIdx.y : blockIdx.y / p.v_rep;
+    const int vh = p.v_all ? 0 : (p.v_rep > 1 ? blockIdx.y - kvh * p.v_rep : kvh);
     const int tile = blockIdx.x / p.n_splits, split = blockIdx.x - tile * p.n_splits;
     const int slot = p.row_slot[b];
     if (slot < 0) return;
@@ -102,8 +105,8 @@ attn_tile_kernel(const AttnParams p) {
     float* p_s = q_s + q_rows_alloc(d, dv) * d;                       // [RMAX][KT]
     float* alpha_s = p_s + RMAX * KT;                                 // [RMAX]
     float* l_s = alpha_s + RMAX;                                      // [RMAX]
-    T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [KT][dv]
-    T* k_s = v_s + KT * dv;                                           // [KT][d + KPAD]
+    T* v_s = reinterpret_cast<T*>(l_s + RMAX);                        // [VR][KT][dv]
+    T* k_s = v_s + VR * KT * dv;                                      // [KT][d + KPAD]
 
     __shared__ int row_s[KT];                    // per token of the tile: its row in the pools, -1 outside [lo, hi)
     __shared__ int vrow_s[KT];
@@ -163,7 +166,7 @@ attn_tile_kernel(const AttnParams p) {
         __syncthreads();
         {
             constexpr int UNR = 4;
-            const int per_tok = cpr + cprv, total = KT * per_tok;
+            const int per_tok = cpr + cprv * VR, total = KT * per_tok;
             for (int c0 = tid; c0 < total; c0 += ATT_THREADS * UNR) {
                 uint4 x4[UNR];
 #pragma unroll
@@ -173,9 +176,12 @@ attn_tile_kernel(const AttnParams p) {
                     if (c < total) {
                         const int tt = c / per_tok, cc = c - tt * per_tok;
                         const int base = row_s[tt];
-                        if (base >= 0)
-                            x4[u] = cc >= cpr ? *reinterpret_cast<const uint4*>(vp + (size_t)vrow_s[tt] * dv + (cc - cpr) * EPC)
+                        if (base >= 0) {
+                            const int cv = cc - cpr, j = cv >= 0 ? cv / cprv : 0;       // value head j's row: j * bs rows on
+                            x4[u] = cc >= cpr ? *reinterpret_cast<const uint4*>(vp + ((size_t)vrow_s[tt] + (size_t)j * bs) * dv +
+                                                                                (cv - j * cprv) * EPC)
                                               : *reinterpret_cast<const uint4*>(kp + (size_t)base * d + cc * EPC);
+                        }
                     }
                 }
 #pragma unroll
@@ -184,7 +190,8 @@ attn_tile_kernel(const AttnParams p) {
                     if (c < total) {
                         const int tt = c / per_tok, cc = c - tt * per_tok;
                         if (cc >= cpr) {
-                            *reinterpret_cast<uint4*>(v_s + tt * dv + (cc - cpr) * EPC) = x4[u];
+                            const int cv = cc - cpr, j = cv / cprv;
+                            *reinterpret_cast<uint4*>(v_s + (j * KT + tt) * dv + (cv - j * cprv) * EPC) = x4[u];
                         } else {
                             uint2* kd = reinterpret_cast<uint2*>(k_s + tt * kstride + cc * EPC);
                             kd[0] = make_uint2(x4[u].x, x4[u].y);
@@ -245,7 +252,27 @@ attn_tile_kernel(const AttnParams p) {
         __syncthreads();
 
         // values: acc[r][dims] = acc * alpha + sum_t p[r][t] * v[t][dims]
-        if (pv_active) {
+        if (pv_active && VR > 1) {
+            // rows R * j + r stand for query row r on value head j: all threads have work although R is small
+#pragma unroll
+            for (int i = 0; i < RPT_MAX; ++i) {
+                const int rv = rg + i * RG;
+                if (rv >= R * VR) break;
+                const int j = rv / R, r = rv - j * R;
+                const float a = alpha_s[r];
+                acc[i][0] *= a; acc[i][1] *= a; acc[i][2] *= a; acc[i][3] *= a;
+                const T* vj = v_s + (size_t)j * KT * dv + dc * 4;
+                for (int tt = 0; tt < KT; ++tt) {
+                    float vf[4];
+                    load_chunk4<T>(vj + tt * dv, vf);
+                    const float pr = p_s[r * KT + tt];
+                    acc[i][0] = fmaf(pr, vf[0], acc[i][0]);
+                    acc[i][1] = fmaf(pr, vf[1], acc[i][1]);
+                    acc[i][2] = fmaf(pr, vf[2], acc[i][2]);
+                    acc[i][3] = fmaf(pr, vf[3], acc[i][3]);
+                }
+            }
+        } else if (pv_active) {
 #pragma unroll
             for (int i = 0; i < RPT_MAX; ++i) {
                 const int r = rg + i * RG;
@@ -284,12 +311,13 @@ attn_tile_kernel(const AttnParams p) {
     T* og = static_cast<T*>(p.out);
 #pragma unroll
     for (int i = 0; i < RPT_MAX; ++i) {
-        const int r = rg + i * RG;
-        if (r >= R) continue;
+        const int rv = rg + i * RG;
+        if (rv >= R * VR) continue;
+        const int jv = rv / R, r = rv - jv * R;
         const int qi = r / G, g = r - qi * G;
         const int head = kvh * G + g;
         size_t row = (size_t)(tok0 + qi) * p.n_q + head;
-        if (p.v_rep > 1) row = row * p.v_rep + vh;
+        if (p.v_rep > 1) row = row * p.v_rep + vh + jv;
         if (p.n_splits > 1) {
             const size_t pi = row * p.n_splits + split;
             if (dc == 0) { p.part_m[pi] = alpha_s[r]; p.part_l[pi] = l_s[r]; }
@@ -383,14 +411,18 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
 }
 
 template <typename T>
-static size_t attn_smem_bytes(int d, int dv) {
+static size_t attn_smem_bytes(int d, int dv, int vr = 1) {
     return (size_t)(q_rows_alloc(d, dv) * d + RMAX * KT + 2 * RMAX) * sizeof(float) +
-           (size_t)(KT * dv + KT * (d + Pad<T>::v)) * sizeof(T);
+           (size_t)(vr * KT * dv + KT * (d + Pad<T>::v)) * sizeof(T);
 }
 
 template <typename T>
-static int launch_attn(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
-    const size_t smem = attn_smem_bytes<T>(p.d, p.dv);
+static int launch_attn(const AttnParams& p0, int n_rows, int max_q_len, cudaStream_t stream) {
+    AttnParams p = p0;
+    // few query rows and repeated value heads: one CTA per key head takes all value heads, if their tiles fit
+    p.v_all = p.v_rep > 1 && p.QT * p.G * p.v_rep <= RMAX && p.d <= 256 && p.dv <= 256 &&
+              attn_smem_bytes<T>(p.d, p.dv, p.v_rep) <= 160 * 1024;
+    const size_t smem = attn_smem_bytes<T>(p.d, p.dv, p.v_all ? p.v_rep : 1);
     auto k = attn_tile_kernel<T>;
     static size_t configured = 0;
     if (smem > configured) {
@@ -399,7 +431,7 @@ static int launch_attn(const AttnParams& p, int n_rows, int max_q_len, cudaStrea
         configured = smem;
     }
     const int q_tiles = (max_q_len + p.QT - 1) / p.QT;
-    dim3 grid(q_tiles * p.n_splits, p.n_kv * p.v_rep, n_rows);
+    dim3 grid(q_tiles * p.n_splits, p.v_all ? p.n_kv : p.n_kv * p.v_rep, n_rows);
     k<<<grid, ATT_THREADS, smem, stream>>>(p);
     return check_launch("attention");
 }
@@ -480,7 +512,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;
     p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d; p.dv = dv; p.chunk = chunk;
     p.n_kv_pool = n_kv; p.kv_div = 1;
-    p.softcap = softcap; p.keep_first = keep_first; p.sink = sink; p.v_rep = v_rep; p.out_f32 = out_f32;
+    p.softcap = softcap; p.keep_first = keep_first; p.sink = sink; p.v_rep = v_rep; p.out_f32 = out_f32; p.v_all = 0;
     if (dv != d) use_mma = 0;          // the tensor-core kernels keep keys and values of one size
     int qt = fd_attn_simt_qt(G);
     if ((d > 256 || dv > 256) && qt > RWIDE / G) qt = RWIDE / G;
