@@ -13,8 +13,8 @@
 //
 // The EXT form of the kernel has the options of the CUDA-core kernel as well: scores capped by a tanh, a window that
 // also keeps the first positions (the key tiles between those and the window's start are not visited), a keyless term
-// per head in the softmax denominator, and weights that are applied to every value head (grid.y = head * v_rep + value
-// head, out [T, n_q, v_rep, D]), written as float on request.  Its weights reach the second product as a sum of two
+// per head in the softmax denominator, and weights that are applied to every value head (a CTA takes VR of them at a
+// time, its scores and softmax worked out once; out [T, n_q, v_rep, D]), written as float on request.  Its weights reach the second product as a sum of two
 // bfloat16 numbers (the rounded weight and what the rounding took away), so they carry 16 bits of mantissa and not 8.
 #include <math.h>
 
@@ -28,7 +28,7 @@ constexpr int PM_THREADS = PM_WARPS * 32;
 constexpr int PM_BM = 64;     // query rows per CTA
 constexpr int PM_BN = 64;     // keys per tile
 
-template <int D, bool EXT>
+template <int D, bool EXT, int VR>
 __global__ void __launch_bounds__(PM_THREADS)
 attn_prefill_mma_kernel(const AttnParams p) {
     constexpr int CPR = D / 8;                      // 16-byte chunks per row
@@ -36,8 +36,10 @@ attn_prefill_mma_kernel(const AttnParams p) {
     // the last query tiles of a sequence see the most keys: schedule them first, so that the
     // short tiles fill the tail of the launch instead of the long ones
     const int tile = gridDim.x - 1 - blockIdx.x, b = blockIdx.z;
-    const int h = EXT ? blockIdx.y / p.v_rep : blockIdx.y;                   // query head
-    const int vhi = EXT ? blockIdx.y - h * p.v_rep : 0;
+    // grid.y = query head * groups of VR value heads + group: the CTA's weights meet VR value heads, scores worked out once
+    const int v_groups = EXT ? p.v_rep / VR : 1;
+    const int h = EXT ? blockIdx.y / v_groups : blockIdx.y;                  // query head
+    const int vhi = EXT ? (blockIdx.y - h * v_groups) * VR : 0;              // first of its value heads
     const int slot = p.row_slot[b];
     if (slot < 0) return;
     const int q_len = p.row_q_len[b];
@@ -46,7 +48,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const int tok0 = p.row_q_start[b] + tile * PM_BM;
     const int nq = min(PM_BM, q_len - tile * PM_BM);
     const int kvh = h / p.G;
-    const int vh = (EXT && p.v_rep > 1) ? vhi : kvh;                         // the head whose values the weights meet
+    const int vh = (EXT && p.v_rep > 1) ? vhi : kvh;                         // the (first) head whose values the weights meet
     const int keep = (EXT && p.window > 0) ? p.keep_first : 0;               // first positions that stay visible
     const float softcap = p.softcap;
     const int p_first = ctx + tile * PM_BM;          // position of this CTA's first query
@@ -57,7 +59,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                        // [64][D]
     unsigned char* k_s = q_s + PM_BM * D * 2;         // [2][64][D]
-    unsigned char* v_s = k_s + 2 * TILE_BYTES;        // [2][64][D]
+    unsigned char* v_s = k_s + 2 * TILE_BYTES;        // [2][VR][64][D]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const __nv_bfloat16* qg = static_cast<const __nv_bfloat16*>(p.q);
@@ -77,7 +79,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
     }
     auto issue = [&](int t0, int stage) {
         unsigned char* ks = k_s + stage * TILE_BYTES;
-        unsigned char* vs = v_s + stage * TILE_BYTES;
+        unsigned char* vs = v_s + stage * VR * TILE_BYTES;
 #pragma unroll
         for (int i = 0; i < PM_BN * CPR / PM_THREADS; ++i) {
             const int c = i * PM_THREADS + tid;
@@ -85,6 +87,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
             const int t = t0 + r;
             const __nv_bfloat16* ksrc = kp;
             const __nv_bfloat16* vsrc = vp;
+            size_t v_head_step = 0;                   // elements from one value head's row to the next one's
             int bytes = 0;
             if ((t >= lo || (EXT && t < keep)) && t < hi) {
                 const int col = bs_shift >= 0 ? t >> bs_shift : t / bs;
@@ -96,11 +99,14 @@ attn_prefill_mma_kernel(const AttnParams p) {
                     const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
                     ksrc = kp + off;
                     vsrc = EXT ? vp + (((size_t)blk * p.n_kv + vh) * bs + in_blk) * D + cc * 8 : vp + off;
+                    v_head_step = (size_t)bs * D;
                     bytes = 16;
                 }
             }
             cp_async16(smem_u32(ks + swz<D>(r, cc)), ksrc, bytes);
-            cp_async16(smem_u32(vs + swz<D>(r, cc)), vsrc, bytes);
+#pragma unroll
+            for (int j = 0; j < VR; ++j)
+                cp_async16(smem_u32(vs + j * TILE_BYTES + swz<D>(r, cc)), vsrc + j * v_head_step, bytes);
         }
         cp_async_commit();
     };
@@ -115,11 +121,13 @@ attn_prefill_mma_kernel(const AttnParams p) {
 
     // head sizes above 128: the query fragments are read from shared memory for every key tile instead of being kept
     // (with the output tile they would not fit the registers)
-    constexpr bool Q_REGS = D <= 128;
+    constexpr bool Q_REGS = D * VR <= 128;
     uint32_t qf[Q_REGS ? D / 16 : 1][4];
-    float o[D / 8][4];
+    float o[VR][D / 8][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int j = 0; j < VR; ++j)
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) o[j][i][0] = o[j][i][1] = o[j][i][2] = o[j][i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
     const float scale_log2 = p.scale * 1.4426950408889634f;
@@ -149,7 +157,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
                 ldmatrix_x4(smem_u32(q_s + swz<D>(r, ks * 2 + (mi >> 1))), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
         }
         const unsigned char* ks_ = k_s + (it & 1) * TILE_BYTES;
-        const unsigned char* vs_ = v_s + (it & 1) * TILE_BYTES;
+        const unsigned char* vs_ = v_s + (it & 1) * VR * TILE_BYTES;
         // a tile wholly in the future of all rows of this warp contributes nothing
         const bool skip = t0 > w_last || (p.window > 0 && t0 + PM_BN - 1 < w_first - p.window + 1 && !(EXT && t0 < keep)) ||
                           t0 + PM_BN - 1 < cs_first;
@@ -220,9 +228,11 @@ attn_prefill_mma_kernel(const AttnParams p) {
             l_run[0] = l_run[0] * alpha[0] + rs[0];
             l_run[1] = l_run[1] * alpha[1] + rs[1];
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) {
-                o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-            }
+            for (int j = 0; j < VR; ++j)
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) {
+                    o[j][i][0] *= alpha[0]; o[j][i][1] *= alpha[0]; o[j][i][2] *= alpha[1]; o[j][i][3] *= alpha[1];
+                }
             {
                 const int mi = lane >> 3;
 #pragma unroll
@@ -238,16 +248,18 @@ attn_prefill_mma_kernel(const AttnParams p) {
                     }
                     const int r = k2 * 16 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
-                    for (int np = 0; np < D / 16; ++np) {
-                        uint32_t b0, b1, b2, b3;
-                        ldmatrix_x4_trans(smem_u32(vs_ + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
-                        mma_bf16(o[np * 2], pa0, pa1, pa2, pa3, b0, b1);
-                        mma_bf16(o[np * 2 + 1], pa0, pa1, pa2, pa3, b2, b3);
-                        if (EXT) {
-                            mma_bf16(o[np * 2], pb0, pb1, pb2, pb3, b0, b1);
-                            mma_bf16(o[np * 2 + 1], pb0, pb1, pb2, pb3, b2, b3);
+                    for (int j = 0; j < VR; ++j)
+#pragma unroll
+                        for (int np = 0; np < D / 16; ++np) {
+                            uint32_t b0, b1, b2, b3;
+                            ldmatrix_x4_trans(smem_u32(vs_ + j * TILE_BYTES + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
+                            mma_bf16(o[j][np * 2], pa0, pa1, pa2, pa3, b0, b1);
+                            mma_bf16(o[j][np * 2 + 1], pa0, pa1, pa2, pa3, b2, b3);
+                            if (EXT) {
+                                mma_bf16(o[j][np * 2], pb0, pb1, pb2, pb3, b0, b1);
+                                mma_bf16(o[j][np * 2 + 1], pb0, pb1, pb2, pb3, b2, b3);
+                            }
                         }
-                    }
                 }
             }
         }
@@ -272,26 +284,29 @@ attn_prefill_mma_kernel(const AttnParams p) {
             l = l * f + exp2f(sk - m2);
         }
         const float inv = l > 0.f ? f / l : 0.f;
-        const size_t orow_i = EXT ? ((size_t)(tok0 + r) * p.n_q + h) * p.v_rep + vhi : (size_t)(tok0 + r) * p.n_q + h;
-        if (EXT && p.out_f32) {
-            float* orow = static_cast<float*>(p.out) + orow_i * D + (lane & 3) * 2;
+#pragma unroll
+        for (int j = 0; j < VR; ++j) {
+            const size_t orow_i = EXT ? ((size_t)(tok0 + r) * p.n_q + h) * p.v_rep + vhi + j : (size_t)(tok0 + r) * p.n_q + h;
+            if (EXT && p.out_f32) {
+                float* orow = static_cast<float*>(p.out) + orow_i * D + (lane & 3) * 2;
+#pragma unroll
+                for (int nt = 0; nt < D / 8; ++nt)
+                    *reinterpret_cast<float2*>(orow + nt * 8) = make_float2(o[j][nt][hh * 2] * inv, o[j][nt][hh * 2 + 1] * inv);
+                continue;
+            }
+            __nv_bfloat16* orow = og + orow_i * D + (lane & 3) * 2;
 #pragma unroll
             for (int nt = 0; nt < D / 8; ++nt)
-                *reinterpret_cast<float2*>(orow + nt * 8) = make_float2(o[nt][hh * 2] * inv, o[nt][hh * 2 + 1] * inv);
-            continue;
+                *reinterpret_cast<__nv_bfloat162*>(orow + nt * 8) =
+                    __floats2bfloat162_rn(o[j][nt][hh * 2] * inv, o[j][nt][hh * 2 + 1] * inv);
         }
-        __nv_bfloat16* orow = og + orow_i * D + (lane & 3) * 2;
-#pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt)
-            *reinterpret_cast<__nv_bfloat162*>(orow + nt * 8) =
-                __floats2bfloat162_rn(o[nt][hh * 2] * inv, o[nt][hh * 2 + 1] * inv);
     }
 }
 
-template <int D, bool EXT>
+template <int D, bool EXT, int VR = 1>
 static int launch_pm(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(PM_BM + 4 * PM_BN) * D * 2;
-    auto k = attn_prefill_mma_kernel<D, EXT>;
+    constexpr size_t smem = (size_t)(PM_BM + 2 * PM_BN + 2 * VR * PM_BN) * D * 2;
+    auto k = attn_prefill_mma_kernel<D, EXT, VR>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -299,7 +314,7 @@ static int launch_pm(const AttnParams& p, int n_rows, int max_q_len, cudaStream_
         configured = true;
     }
     const int q_tiles = (max_q_len + PM_BM - 1) / PM_BM;
-    const int heads = EXT ? p.n_q * p.v_rep : p.n_q;
+    const int heads = EXT ? p.n_q * (p.v_rep / VR) : p.n_q;
     if (heads > 65535 || n_rows > 65535) return 1;
     dim3 grid(q_tiles, heads, n_rows);
     k<<<grid, PM_THREADS, smem, stream>>>(p);
@@ -320,8 +335,12 @@ int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cuda
 // not take.
 int launch_attn_prefill_mma_ext(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream) {
     if (p.n_splits != 1 || p.d != p.dv || p.chunk > 0) return 1;
-    if (p.d == 128) return launch_pm<128, true>(p, n_rows, max_q_len, stream);
-    if (p.d == 64) return launch_pm<64, true>(p, n_rows, max_q_len, stream);
+    // repeated value heads: a CTA takes two of them (four of 64 dimensions), as many as its registers hold outputs for
+    if (p.d == 128) return p.v_rep % 2 == 0 ? launch_pm<128, true, 2>(p, n_rows, max_q_len, stream)
+                                            : launch_pm<128, true, 1>(p, n_rows, max_q_len, stream);
+    if (p.d == 64) return p.v_rep % 4 == 0   ? launch_pm<64, true, 4>(p, n_rows, max_q_len, stream)
+                          : p.v_rep % 2 == 0 ? launch_pm<64, true, 2>(p, n_rows, max_q_len, stream)
+                                             : launch_pm<64, true, 1>(p, n_rows, max_q_len, stream);
     return 1;
 }
 
