@@ -38,7 +38,6 @@
 namespace fd {
 
 constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_RPT = 32;           // state rows a thread holds at most
 
 struct ScanParams {
     const void* proj; int ld;          // [T, ld]
@@ -65,7 +64,9 @@ __device__ __forceinline__ int seg_slot(int q_start, int seg_len, int r, int s) 
 
 // Shared-memory place of channel i of a token: a thread's NR rows are adjacent (read four at a time), and the DS groups
 // of rows are NR + 4 floats apart so that the DS lanes of a column read different banks.
-template <int NR> __device__ __forceinline__ int chan_at(int i) { return (i / NR) * (NR + 4) + (i % NR); }
+template <int NR> __host__ __device__ constexpr int chan_stride() { return NR == 4 ? 4 : NR + 4; }
+template <int NR> __device__ __forceinline__ int chan_at(int i) { return (i / NR) * chan_stride<NR>() + (i % NR); }
+constexpr int SCAN_COLS = 4;           // adjacent value columns a thread holds
 
 // q, b (and a) of n tokens from `tok0` on (the first at position pos0), as floats: token tt's q goes to
 // dst + tt * tok_stride + chan_at(i), its b CS floats further and its a 2 CS floats further.  A thread's loads of several
@@ -145,7 +146,7 @@ scan_prepare_kernel(const ScanParams p) {
     const int t0 = seg * p.seg_len + part * PREP_TOKENS;
     if (t0 >= q_len) return;
     const int n = min(PREP_TOKENS, q_len - t0);
-    const int DP = p.DS * NR, CS = p.DS * (NR + 4);
+    const int DP = p.DS * NR, CS = p.DS * chan_stride<NR>();
     const size_t TS = (size_t)(p.mode ? 3 : 2) * CS;
     stage_tokens<T, NR>(p, h, q_start + t0, ctx + t0, n, p.prep + ((size_t)(q_start + t0) * p.H + h) * TS, p.H * TS, DP, CS,
                         threadIdx.x, PREP_THREADS, h == 0);
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(const ScanParams p) {
     // blockIdx.x = (row * segments + segment) * tiles + tile of value columns
     const int DS = p.DS, TC = p.TC;
-    const int VT = SCAN_THREADS / DS;
+    const int VT = SCAN_THREADS / DS * SCAN_COLS;
     const int tiles = (p.dv + VT - 1) / VT;
     const int rs = blockIdx.x / tiles, tile = blockIdx.x - rs * tiles;
     const int r = rs / p.n_seg, seg = rs - r * p.n_seg, h = blockIdx.y;
@@ -177,29 +178,30 @@ linear_scan_kernel(const ScanParams p) {
     const int sslot = PHASE == 0 ? 0 : seg_slot(q_start, p.seg_len, r, seg);
     const int d = p.d, dv = p.dv;
     const int DP = DS * NR;                          // channels with the padding (their q, a and b are zero)
-    const int CS = DS * (NR + 4);                    // floats of one of a token's q, b and a in shared memory
+    const int CS = DS * chan_stride<NR>();                    // floats of one of a token's q, b and a in shared memory
     const int TS = (p.mode ? 3 : 2) * CS;            // floats of a token's q, b (and a)
     const int BUF = TC * (TS + VT);                  // floats of a chunk: [TC][TS], then v [TC][VT]
     const int tid = threadIdx.x;
     const int vl = tid / DS, ds = tid - vl * DS;
-    const int v = tile * VT + vl;
-    const bool v_ok = v < dv;
+    const int v0 = tile * VT + vl * SCAN_COLS;       // the thread's columns v0 .. v0 + 3
 
     extern __shared__ __align__(16) float sm[];     // one chunk (PHASE 0) or two, filled in turn
 
     float* st = p.state + ((size_t)slot * p.H + h) * d * dv;
     // a segment after the first starts from what the chaining left in the slot of the segment before it
     const float* st_in = (PHASE == 3 && seg > 0) ? p.seg_state + ((size_t)(sslot - 1) * p.H + h) * d * dv : st;
-    float S[NR];                        // rows ds * NR .. ds * NR + NR - 1 of column v
+    float S[NR][SCAN_COLS];             // rows ds * NR .. ds * NR + NR - 1 of the thread's columns
     float A[PHASE == 1 ? NR : 1];
 #pragma unroll
     for (int ii = 0; ii < NR; ++ii) {
         const int i = ds * NR + ii;
-        S[ii] = (PHASE != 1 && i < d && v_ok) ? st_in[(size_t)i * dv + v] : 0.f;
+#pragma unroll
+        for (int c = 0; c < SCAN_COLS; ++c)
+            S[ii][c] = (PHASE != 1 && i < d && v0 + c < dv) ? st_in[(size_t)i * dv + v0 + c] : 0.f;
         if (PHASE == 1) A[ii] = 1.f;
     }
     const float g = p.mode == 0 ? p.decay[h] : 0.f;
-    const int my = ds * (NR + 4);
+    const int my = ds * chan_stride<NR>();
 
     // segments copy what the preparing kernel left, a chunk ahead of the one that is walked
     auto issue = [&](int c0, int buf) {
@@ -247,34 +249,46 @@ linear_scan_kernel(const ScanParams p) {
         }
         const float* v_s = buf + TC * TS;
         for (int tt = 0; tt < n; ++tt) {
-            const float vv = v_s[tt * VT + vl];
+            const float4 vv = *reinterpret_cast<const float4*>(v_s + tt * VT + vl * SCAN_COLS);
             const float4* qr = reinterpret_cast<const float4*>(buf + tt * TS + my);
             const float4* br = reinterpret_cast<const float4*>(buf + tt * TS + CS + my);
             const float4* ar = reinterpret_cast<const float4*>(buf + tt * TS + 2 * CS + my);
-            float o4[4] = {0.f, 0.f, 0.f, 0.f};
+            float o[SCAN_COLS] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NR / 4; ++j) {
                 const float4 b4 = br[j];
                 float4 a4 = make_float4(g, g, g, g), q4 = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (p.mode == 1) a4 = ar[j];
                 if (PHASE != 1) q4 = qr[j];
-                S[4 * j + 0] = fmaf(a4.x, S[4 * j + 0], b4.x * vv);
-                S[4 * j + 1] = fmaf(a4.y, S[4 * j + 1], b4.y * vv);
-                S[4 * j + 2] = fmaf(a4.z, S[4 * j + 2], b4.z * vv);
-                S[4 * j + 3] = fmaf(a4.w, S[4 * j + 3], b4.w * vv);
-                if (PHASE == 1) {
-                    if (p.mode == 1) { A[4 * j + 0] *= a4.x; A[4 * j + 1] *= a4.y; A[4 * j + 2] *= a4.z; A[4 * j + 3] *= a4.w; }
-                } else {
-                    o4[0] = fmaf(S[4 * j + 0], q4.x, o4[0]);
-                    o4[1] = fmaf(S[4 * j + 1], q4.y, o4[1]);
-                    o4[2] = fmaf(S[4 * j + 2], q4.z, o4[2]);
-                    o4[3] = fmaf(S[4 * j + 3], q4.w, o4[3]);
+                const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float* Sr = S[4 * j + e];
+                    Sr[0] = fmaf(aa[e], Sr[0], bb[e] * vv.x);
+                    Sr[1] = fmaf(aa[e], Sr[1], bb[e] * vv.y);
+                    Sr[2] = fmaf(aa[e], Sr[2], bb[e] * vv.z);
+                    Sr[3] = fmaf(aa[e], Sr[3], bb[e] * vv.w);
+                    if (PHASE == 1) {
+                        if (p.mode == 1) A[4 * j + e] *= aa[e];
+                    } else {
+                        o[0] = fmaf(Sr[0], qq[e], o[0]);
+                        o[1] = fmaf(Sr[1], qq[e], o[1]);
+                        o[2] = fmaf(Sr[2], qq[e], o[2]);
+                        o[3] = fmaf(Sr[3], qq[e], o[3]);
+                    }
                 }
             }
             if (PHASE != 1) {
-                float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-                for (int off = 1; off < DS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-                if (ds == 0 && v_ok) p.out[(size_t)(q_start + c0 + tt) * p.H * dv + h * dv + v] = o;
+                for (int off = 1; off < DS; off <<= 1) {
+#pragma unroll
+                    for (int c = 0; c < SCAN_COLS; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], off);
+                }
+                if (ds == 0) {
+                    float* orow = p.out + (size_t)(q_start + c0 + tt) * p.H * dv + h * dv + v0;
+#pragma unroll
+                    for (int c = 0; c < SCAN_COLS; ++c)
+                        if (v0 + c < dv) orow[c] = o[c];
+                }
             }
         }
         if (PHASE != 0) __syncthreads();             // the chunk is through before its place is filled again
@@ -285,16 +299,22 @@ linear_scan_kernel(const ScanParams p) {
 #pragma unroll
         for (int ii = 0; ii < NR; ++ii) {
             const int i = ds * NR + ii;
-            if (i < d && v_ok) u[(size_t)i * dv + v] = S[ii];
-            if (i < d && p.mode == 1 && tile == 0 && vl == 0) a[i] = A[ii];
+            if (i >= d) continue;
+#pragma unroll
+            for (int c = 0; c < SCAN_COLS; ++c)
+                if (v0 + c < dv) u[(size_t)i * dv + v0 + c] = S[ii][c];
+            if (p.mode == 1 && tile == 0 && vl == 0) a[i] = A[ii];
         }
         return;
     }
-    if (p.write_state && v_ok && last_seg) {
+    if (p.write_state && last_seg) {
 #pragma unroll
         for (int ii = 0; ii < NR; ++ii) {
             const int i = ds * NR + ii;
-            if (i < d) st[(size_t)i * dv + v] = S[ii];
+            if (i >= d) continue;
+#pragma unroll
+            for (int c = 0; c < SCAN_COLS; ++c)
+                if (v0 + c < dv) st[(size_t)i * dv + v0 + c] = S[ii][c];
         }
     }
 }
@@ -362,16 +382,16 @@ constexpr int SCAN_SEG = 64;           // tokens of a segment
 template <typename T, int NR>
 static int scan_launches(const ScanParams& base, int n_rows, cudaStream_t stream) {
     ScanParams p = base;
-    const int VT = SCAN_THREADS / p.DS;
+    const int VT = SCAN_THREADS / p.DS * SCAN_COLS;
     const dim3 block(SCAN_THREADS), one(1, 1, 1);
     const unsigned tiles = (p.dv + VT - 1) / VT;
     if (p.n_seg <= 1) {
         p.phase = 0; p.n_seg = 1;
-        const size_t smem = (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * (NR + 4) + VT) * sizeof(float);
+        const size_t smem = (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * chan_stride<NR>() + VT) * sizeof(float);
         return launch("linear_scan", linear_scan_kernel<T, 0, NR>, dim3(tiles * n_rows, p.H, 1), block, smem, stream, one, p);
     }
     p.TC = p.d <= 128 ? 8 : 4;             // two chunks in shared memory, one of them in flight
-    const size_t smem = 2 * (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * (NR + 4) + VT) * sizeof(float);
+    const size_t smem = 2 * (size_t)p.TC * ((p.mode ? 3 : 2) * p.DS * chan_stride<NR>() + VT) * sizeof(float);
     int rc = launch("linear_scan_prepare", scan_prepare_kernel<T, NR>,
                     dim3(n_rows * p.n_seg * (p.seg_len / PREP_TOKENS), p.H, 1), dim3(PREP_THREADS), 0, stream, one, p);
     if (rc) return rc;
@@ -386,26 +406,28 @@ static int scan_launches(const ScanParams& base, int n_rows, cudaStream_t stream
     return launch("linear_scan", linear_scan_kernel<T, 3, NR>, grid, block, smem, stream, one, p);
 }
 
-static int scan_ds(int d) { return d <= 4 * SCAN_RPT ? 4 : 8; }
-static int scan_nr(int d) {
-    const int rows = (d + scan_ds(d) - 1) / scan_ds(d);        // state rows a thread holds
-    return rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+// A thread holds NR adjacent rows of four columns; DS lanes share those columns: 8 rows and 16 or 32 lanes for the
+// larger heads, 4 rows and as many lanes as cover d for heads up to 64.
+static int scan_nr(int d) { return d > 64 ? 8 : 4; }
+static int scan_ds(int d) {
+    int ds = 4;
+    while (ds * scan_nr(d) < d) ds *= 2;
+    return ds;
 }
 
 template <typename T>
 static int scan_by_rows(const ScanParams& p, int n_rows, cudaStream_t stream) {
-    const int nr = scan_nr(p.d);
-    if (nr == 8) return scan_launches<T, 8>(p, n_rows, stream);
-    if (nr == 16) return scan_launches<T, 16>(p, n_rows, stream);
-    return scan_launches<T, 32>(p, n_rows, stream);
+    if (scan_nr(p.d) == 8) return scan_launches<T, 8>(p, n_rows, stream);
+    return scan_launches<T, 4>(p, n_rows, stream);
 }
 
 // Tokens of a segment, and the floats of scratch memory that a step of T tokens in n_rows sequences needs to run its
-// recurrences in segments: the prepared q, b, a (three places of DS * (NR + 4) floats per token and head) and v, then
+// recurrences in segments: the prepared q, b, a (three places of DS * chan_stride<NR>() floats per token and head) and v, then
 // states and gate products of T / segment + n_rows + 1 segment slots.
 extern "C" int fd_linear_scan_segment() { return SCAN_SEG; }
+static int scan_chan_floats(int d) { return scan_ds(d) * (scan_nr(d) == 4 ? 4 : scan_nr(d) + 4); }
 static long long scan_prep_floats(int T, int H, int d, int dv) {
-    return (long long)T * H * (3 * scan_ds(d) * (scan_nr(d) + 4) + (dv + 3) / 4 * 4);
+    return (long long)T * H * (3 * scan_chan_floats(d) + (dv + 3) / 4 * 4);
 }
 extern "C" long long fd_linear_scan_scratch_floats(int T, int n_rows, int H, int d, int dv) {
     return scan_prep_floats(T, H, d, dv) + (long long)(T / SCAN_SEG + n_rows + 1) * H * ((long long)d * dv + d);
@@ -423,8 +445,7 @@ extern "C" int fd_linear_scan(const void* proj, int ld, int dtype, int q_col, in
                               int d, int dv, int write_state, int* status, int T, int max_q_len, float* scratch,
                               long long scratch_floats, cudaStream_t stream) {
     if (n_rows == 0) return 0;
-    FD_REQUIRE(H > 0 && d > 0 && dv > 0 && d <= 8 * SCAN_RPT, -2, "linear_scan: %d heads of %d x %d (d at most %d)", H, d,
-               dv, 8 * SCAN_RPT);
+    FD_REQUIRE(H > 0 && d > 0 && dv > 0 && d <= 256, -2, "linear_scan: %d heads of %d x %d (d at most 256)", H, d, dv);
     FD_REQUIRE(mode == 0 || mode == 1, -2, "linear_scan: unknown mode %d", mode);
     FD_REQUIRE(mode == 1 ? lower != nullptr : decay != nullptr, -2, "linear_scan: the mode's constants are missing");
     FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d && (rot == 0 || mode == 1 || (cos_t && sin_t)), -2,
@@ -447,7 +468,7 @@ extern "C" int fd_linear_scan(const void* proj, int ld, int dtype, int q_col, in
         p.n_seg = (max_q_len + SCAN_SEG - 1) / SCAN_SEG;
         FD_REQUIRE((uintptr_t)scratch % 16 == 0, -2, "linear_scan: scratch memory must be 16-byte aligned");
         p.prep = scratch;
-        p.prep_v = scratch + (long long)T * H * (mode ? 3 : 2) * p.DS * (scan_nr(d) + 4);
+        p.prep_v = scratch + (long long)T * H * (mode ? 3 : 2) * scan_chan_floats(d);
         p.seg_state = scratch + scan_prep_floats(T, H, d, dv);
         p.seg_decay = p.seg_state + slots * H * d * dv;
     }
