@@ -182,8 +182,10 @@ class ConvGatedAttention(Mixer):
                 split_len = FP32_SPLIT_LEN
                 n_splits = max(1, -(-ctx.kv_len_bound // split_len))
             else:
-                n_splits, split_len = plan_splits(ctx.n_rows, heads_out // (self.n_q // self.n_kv), ctx.kv_len_bound,
-                                                  rt.sm_count)
+                # CTAs per sequence and split: one per key head and value head it meets, or - mixed heads of up to 64
+                # query rows in all - one per key head, which takes all value heads
+                per_seq = self.n_kv if self.talk and self.n_q <= 64 else heads_out // (self.n_q // self.n_kv)
+                n_splits, split_len = plan_splits(ctx.n_rows, per_seq, ctx.kv_len_bound, rt.sm_count)
             if n_splits > 1:
                 scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, heads_out, self.dv, n_splits),),
                                  torch.float32)
