@@ -685,6 +685,43 @@ def test_configurations_drawn_at_random_in_bfloat16(tmp_path, seed):
     eng.model.check_status()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_at_sizes_of_the_tensor_core_kernels(tmp_path, dtype):
+    """Heads of 64 on every mixer, prompts of several hundred tokens: many segments of the recurrences, key tiles
+    between the kept positions and the window that are never visited, two value heads in one CTA; every position of
+    each prompt alone, then the two together and decoded on."""
+    import revelix_helpers as H
+    rot = H._rot(32, 10000.0, (4.0, 64, 16.0, 1.0))
+    att = H.attention(4, 2, 64, 64, 3, 0.125, softcap=15.0, window=150, keep_first=20, rot=rot)
+    cfg = H.model(333, 128, 1e-5, [
+        H.retention(2, 64, 64, [0.97, 0.999], H._rot(64, 10000.0), H.dense(96)),
+        H.parallel(att, H.recurrence(2, 64, 32), 0.7, 1.2, H.dense(96)),
+        H.retention(3, 128, 32, [0.9, 0.99, 1.0], H._rot(16, 100.0)),
+        H.parallel(att, H.recurrence(1, 128, 64), mlp=H.dense(40))], logit_scale=0.5)
+    folder = fd.write_random_model(tmp_path / "m", cfg, 7)
+    W = weights_of(folder)
+    cfg = raw_config(folder)
+    reqs = prompts_for(cfg["vocab"], [610, 333], seed=7)
+    want = [Truth(cfg, W, r) for r in reqs]
+    eng = fd.load(folder, device="cuda", dtype=dtype)
+    cache = eng.model.new_cache(max_tokens=1024, max_slots=4, slack_blocks=4, block_size=64)
+    for r, w in zip(reqs, want):
+        s = cache.admit()
+        assert w.excess(eng.model.step(cache, [s], [r], "all"), range(len(r)), dtype) < 1, f"prompt of {len(r)} tokens"
+        cache.release(s)
+    slots = [cache.admit() for _ in reqs]
+    heads = [600, 325]
+    got = eng.model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], "last")
+    for i in range(2):
+        assert want[i].excess(got[i], [heads[i] - 1], dtype) < 1
+    for step in range(8):
+        got = eng.model.step(cache, slots, [[reqs[i][heads[i] + step]] for i in range(2)], "last")
+        for i in range(2):
+            assert want[i].excess(got[i], [heads[i] + step], dtype) < 1, (i, step)
+    eng.model.check_status()
+    cache.check_invariants()
+
+
 @pytest.mark.parametrize("name", NAMES)
 def test_greedy_generation_through_the_engine(folders, name):
     """``Engine.generate``: the scheduler admits five requests three at a time, decode steps replay captured graphs."""
