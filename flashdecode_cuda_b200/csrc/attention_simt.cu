@@ -562,6 +562,33 @@ __global__ void attn_head_mix_kernel(const float* __restrict__ o, const float* _
     }
 }
 
+// The same with a CTA per token and key/value head: the other heads' outputs on that value head (n_q x dv floats) and the
+// group's rows of the mixing matrix are brought to shared memory once, with all loads in flight together, and the G heads
+// of the group are summed from there.  Same order of additions as the kernel above.
+template <typename T>
+__global__ void attn_head_mix_staged_kernel(const float* __restrict__ o, const float* __restrict__ mix, T* __restrict__ out,
+                                            int ld_out, int n_q, int n_kv, int dv, float scale) {
+    extern __shared__ __align__(16) float mix_sm[];
+    const int t = blockIdx.y, vh = blockIdx.x;
+    const int G = n_q / n_kv;
+    float* o_s = mix_sm;                    // [n_q][dv]
+    float* m_s = o_s + n_q * dv;            // [G][n_q]
+    const float* ot = o + (size_t)t * n_q * n_kv * dv;
+    const int dv4 = dv >> 2;
+    for (int e = threadIdx.x; e < n_q * dv4; e += blockDim.x) {
+        const int g = e / dv4, c = e - g * dv4;
+        reinterpret_cast<float4*>(o_s)[e] = *reinterpret_cast<const float4*>(ot + ((size_t)g * n_kv + vh) * dv + c * 4);
+    }
+    for (int e = threadIdx.x; e < G * n_q; e += blockDim.x) m_s[e] = mix[(size_t)vh * G * n_q + e];
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
+        const int gi = e / dv, j = e - gi * dv;
+        float a = 0.f;
+        for (int g = 0; g < n_q; ++g) a = fmaf(m_s[gi * n_q + g], o_s[g * dv + j], a);
+        out[(size_t)t * ld_out + (vh * G + gi) * dv + j] = from_float<T>(a * scale);
+    }
+}
+
 // The CUDA-core kernel for every case.
 extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                                  const int* block_table, int max_blocks, int num_blocks, int block_size,
@@ -632,6 +659,16 @@ extern "C" int fd_attn_head_mix(const float* o, const float* mix, void* out, int
                                 int n_kv, int dv, float scale, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0 && T <= 65535, -2, "attn_head_mix: %d heads on %d, %d tokens", n_q, n_kv, T);
+    const size_t staged = (size_t)(n_q * dv + n_q / n_kv * n_q) * sizeof(float);
+    if (dv % 4 == 0 && staged <= 48 * 1024 && (uintptr_t)o % 16 == 0) {
+        const int work = n_q / n_kv * dv;
+        const dim3 sgrid(n_kv, T), sblock(work >= 256 ? 256 : (work + 31) / 32 * 32);
+        if (dtype == 0)
+            return launch("attn_head_mix", attn_head_mix_staged_kernel<float>, sgrid, sblock, staged, stream, dim3(1, 1, 1), o,
+                          mix, (float*)out, ld_out, n_q, n_kv, dv, scale);
+        return launch("attn_head_mix", attn_head_mix_staged_kernel<bf16>, sgrid, sblock, staged, stream, dim3(1, 1, 1), o, mix,
+                      (bf16*)out, ld_out, n_q, n_kv, dv, scale);
+    }
     const dim3 grid(n_q, T);
     const int threads = dv >= 128 ? 128 : (dv + 31) / 32 * 32;
     if (dtype == 0)

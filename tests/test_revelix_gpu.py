@@ -441,6 +441,21 @@ def test_capped_windowed_attention_in_portions_and_token_by_token(dtype, case):
     _mixed_attention_case(dtype, d, dv, G, n_kv, window, keep, cap, bs, min(S, 3 * w + keep + 2), [1] * S, seed=3)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,dv,T", [(6, 2, 24, 5), (4, 4, 8, 3), (32, 8, 64, 70), (64, 8, 256, 3), (5, 1, 40, 9)])
+def test_heads_mixed_on_their_own_value_head(dtype, n_q, n_kv, dv, T):
+    """out[t, h] = scale * sum_g mix[h, g] o[t, g, h's value head]; sizes whose rows fit shared memory and one that does not."""
+    torch.manual_seed(n_q + dv)
+    o = torch.randn(T, n_q, n_kv, dv)
+    mix = torch.randn(n_q, n_q)
+    out = torch.full((T, 3 + n_q * dv), 4.0, dtype=TD[dtype], device=DEV)
+    K.attn_head_mix(o.reshape(T, -1).to(DEV), mix.to(DEV), out, 3, n_q, n_kv, dv, 0.7)
+    G = n_q // n_kv
+    want = torch.stack([0.7 * torch.einsum("g,tgj->tj", mix[h].double(), o[:, :, h // G].double()) for h in range(n_q)], dim=1)
+    assert rel_err(out[:, 3:], want.reshape(T, n_q * dv)) < KTOL[dtype]
+    assert bool((out[:, :3] == 4.0).all())
+
+
 def test_sink_takes_its_share_and_nothing_else():
     """One query, one key: the weight of the key is e^s / (e^s + e^sink), so the output is that share of the value;
     with mixing weights of zero off the diagonal a head's output depends on its own sink only."""
