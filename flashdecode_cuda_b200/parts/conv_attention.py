@@ -185,7 +185,16 @@ class ConvGatedAttention(Mixer):
                 # CTAs per sequence and split: one per key head and value head it meets, or - mixed heads of up to 64
                 # query rows in all - one per key head, which takes all value heads
                 per_seq = self.n_kv if self.talk and self.n_q <= 64 else heads_out // (self.n_q // self.n_kv)
-                n_splits, split_len = plan_splits(ctx.n_rows, per_seq, ctx.kv_len_bound, rt.sm_count)
+                # with a window only its keys and the kept ones are read: the splits are sized for those, so that the
+                # CTAs that find keys are about as many as the SMs, and laid over the whole length
+                seen = ctx.kv_len_bound
+                if self.window:
+                    seen = min(seen, self.window + self.keep_first + 32)
+                _, split_len = plan_splits(ctx.n_rows, per_seq, seen, rt.sm_count)
+                n_splits = max(1, -(-ctx.kv_len_bound // split_len))
+                if n_splits > 64:                       # bounded scratch memory and merge
+                    split_len = -(-(-(-ctx.kv_len_bound // 64)) // 32) * 32
+                    n_splits = -(-ctx.kv_len_bound // split_len)
             if n_splits > 1:
                 scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, heads_out, self.dv, n_splits),),
                                  torch.float32)
