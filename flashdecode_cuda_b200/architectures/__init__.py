@@ -1,3 +1,3 @@
 """Architectures this library ships.  Importing the package registers them."""
 
-from . import lonasun, nizazen, qwen2, revelix  # noqa: F401  (registration)
+from . import botusun, lonasun, nizazen, qwen2, revelix  # noqa: F401  (registration)

@@ -12,6 +12,7 @@ from pathlib import Path
 from typing import Any, Dict, List, Union
 
 from ..registry import architecture
+from .botusun import BotusunConfig
 from .lonasun import LonasunConfig
 from .nizazen import NizazenConfig
 from .qwen2 import ConfigError, Qwen2Config
@@ -62,4 +63,4 @@ def load_config(source: Union[str, Path, Dict[str, Any]]):
     raise ConfigError(f"no config.json at {source!r} and no preset of that name; presets: {preset_names()}")
 
 
-__all__ = ["ConfigError", "Qwen2Config", "LonasunConfig", "NizazenConfig", "RevelixConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]
+__all__ = ["ConfigError", "Qwen2Config", "BotusunConfig", "LonasunConfig", "NizazenConfig", "RevelixConfig", "load_config", "config_from_dict", "preset_dict", "preset_names"]

@@ -7,7 +7,10 @@
 //    rotation of the first `rot` dimensions of every q and k head (dimension i
 //    paired with i + rot/2, or, `interleaved`, dimension 2i with 2i + 1) at the
 //    token's position, q to its buffer and k, v to the paged cache (value heads
-//    may have a size of their own);
+//    may have a size of their own).  By option every q and k head is RMS-normed
+//    (a weight vector for q and one for k, shared by the heads) between the
+//    convolution and the rotation, and the values are the convolved keys as
+//    they stand before that norm (no v columns in the projection then);
 //  * conv_state_update: the sequence's state becomes the last taps - 1 projected
 //    values after the step;
 //  * gate_mul: out = a * sigmoid(g), g read with a row stride (the gate columns
@@ -57,16 +60,20 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
                         T* __restrict__ k_pool, T* __restrict__ v_pool,
                         const int* __restrict__ block_table, int max_blocks, int num_blocks,
                         int block_size, int n_q, int n_kv, int d, int dv, int taps, int write_kv,
-                        int update_state, int* status, int n_tok, int tpc, int interleaved) {
+                        int update_state, int* status, int n_tok, int tpc, int interleaved,
+                        const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float norm_eps,
+                        int norm_count, int v_from_k) {
     extern __shared__ float y_s[];                 // [tpc][width]: the head's convolved channels of every token
     __shared__ int m_slot[CONV_TPC], m_start[CONV_TPC], m_i[CONV_TPC], m_pos[CONV_TPC], m_move[CONV_TPC];
+    __shared__ float ss_s[CONV_TPC][4];            // per token and warp: the sum of squares of the head's channels
     __shared__ long long m_dst[CONV_TPC];          // element offset of the token's key or value row of this head, or -1
     const int hu = blockIdx.y;                     // head unit: q heads, then k heads, then v heads
     const int t0 = blockIdx.x * tpc;
     const int nt = min(tpc, n_tok - t0);
-    const int C = (n_q + n_kv) * d + n_kv * dv;
+    const int C = (n_q + n_kv) * d + (v_from_k ? 0 : n_kv * dv);
     const bool is_q = hu < n_q, is_v = hu >= n_q + n_kv;
     const int width = is_v ? dv : d;
+    const float* norm_w = is_q ? q_norm_w : (is_v ? nullptr : k_norm_w);
     const int c0 = is_v ? (n_q + n_kv) * d + (hu - n_q - n_kv) * dv : hu * d;     // the head's first channel
     const int hist = taps - 1;
 
@@ -162,29 +169,51 @@ conv_rope_append_kernel(const T* __restrict__ proj, int ld, const float* __restr
         for (int tt = 0; tt < CONV_TPC; ++tt)
             if (tt < nt) { y_s[tt * width + j] = y0[tt]; y_s[tt * width + j + 1] = y1[tt]; }
     }
+    if (norm_w != nullptr) {                       // every thread: the warps' sums are added in warp order below
+#pragma unroll
+        for (int tt = 0; tt < CONV_TPC; ++tt) {
+            if (tt >= nt) continue;
+            const float s = warp_sum(y0[tt] * y0[tt] + y1[tt] * y1[tt]);
+            if ((threadIdx.x & 31) == 0) ss_s[tt][threadIdx.x >> 5] = s;
+        }
+    }
     __syncthreads();
     if (!active) return;
 
     const int half = rot >> 1;
+    const int n_warps = blockDim.x >> 5;
+    float nw[2] = {1.f, 1.f};
+    if (norm_w != nullptr) { nw[0] = norm_w[j]; nw[1] = norm_w[j + 1]; }
 #pragma unroll
     for (int tt = 0; tt < CONV_TPC; ++tt) {
         if (tt >= nt || m_slot[tt] < 0) continue;
         const int pos = m_pos[tt];
-        float v[2] = {y0[tt], y1[tt]};
+        if (v_from_k && !is_q && m_dst[tt] >= 0)   // the values: the convolved keys before norm and rotation
+            store2(v_pool + m_dst[tt] + j, y0[tt], y1[tt]);
+        float rinv = 1.f;
+        if (norm_w != nullptr) {
+            float total = 0.f;
+            for (int w = 0; w < n_warps; ++w) total += ss_s[tt][w];
+            rinv = rsqrtf(total / (float)norm_count + norm_eps);
+        }
+        const float n0 = y0[tt] * rinv * nw[0], n1 = y1[tt] * rinv * nw[1];
+        float v[2] = {n0, n1};
         if (!is_v && j < rot && pos >= 0 && pos < table_len) {      // q and k heads: rotate the leading `rot` dimensions
             const float* cs = cos_t + (size_t)pos * half;
             const float* sn = sin_t + (size_t)pos * half;
             if (interleaved) {                     // the pair is this thread's own two channels
                 const float c = cs[j >> 1], sv = sn[j >> 1];
-                v[0] = y0[tt] * c - y1[tt] * sv;
-                v[1] = y1[tt] * c + y0[tt] * sv;
+                v[0] = n0 * c - n1 * sv;
+                v[1] = n1 * c + n0 * sv;
             } else {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int je = j + e;
                     if (je >= rot) continue;
-                    if (je < half) v[e] = v[e] * cs[je] - y_s[tt * width + je + half] * sn[je];
-                    else v[e] = v[e] * cs[je - half] + y_s[tt * width + je - half] * sn[je - half];
+                    const int pj = je < half ? je + half : je - half;        // the rotation partner, normed like this one
+                    const float other = y_s[tt * width + pj] * (norm_w != nullptr ? rinv * norm_w[pj] : 1.f);
+                    if (je < half) v[e] = v[e] * cs[je] - other * sn[je];
+                    else v[e] = v[e] * cs[je - half] + other * sn[je - half];
                 }
             }
         }
@@ -268,18 +297,25 @@ typedef __nv_bfloat16 bf16;
 // (n_kv * d) and v (n_kv * dv) side by side from column 0; conv_w [C, taps] and state [slots, taps - 1, C] are float
 // (state may be null when taps == 1).  cos_t / sin_t [table_len, rot / 2] (unused when rot == 0).
 // update_state != 0: rows that bring one token move their state on here; other rows need fd_conv_state_update.
+// q_norm_w / k_norm_w [d] float or null: RMS norm of every q / k head after the convolution (mean over norm_count
+// dimensions, the true head size where d is padded with zero channels).  v_from_k != 0: proj holds no v columns, dv == d,
+// and v_pool receives the convolved keys as they are before norm and rotation.
 extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const float* conv_w, float* state, void* q_out,
                                    const float* cos_t, const float* sin_t, int table_len, int rot,
                                    const int* tok_row, const int* tok_pos, const int* row_slot,
                                    const int* row_q_start, const int* row_q_len, void* k_pool, void* v_pool,
                                    const int* block_table, int max_blocks, int num_blocks, int block_size, int T,
                                    int n_q, int n_kv, int d, int dv, int taps, int write_kv, int update_state,
-                                   int* status, int interleaved, cudaStream_t stream) {
+                                   int* status, int interleaved, const float* q_norm_w, const float* k_norm_w,
+                                   float norm_eps, int norm_count, int v_from_k, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(n_q > 0 && n_kv > 0 && d > 0 && dv > 0 && taps >= 1 && block_size > 0, -2, "conv_rope_append: bad sizes");
     FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, -2, "conv_rope_append: %d rotated dimensions of a head of %d", rot, d);
     FD_REQUIRE(taps == 1 || state != nullptr, -2, "conv_rope_append: %d taps need a state", taps);
-    const int C = (n_q + n_kv) * d + n_kv * dv;
+    FD_REQUIRE(!v_from_k || dv == d, -2, "conv_rope_append: values taken from the keys have their size (%d, not %d)", d, dv);
+    FD_REQUIRE((q_norm_w == nullptr && k_norm_w == nullptr) || (norm_count > 0 && norm_count <= d), -2,
+               "conv_rope_append: a norm over %d of %d dimensions", norm_count, d);
+    const int C = (n_q + n_kv) * d + (v_from_k ? 0 : n_kv * dv);
     FD_REQUIRE(ld >= C, -2, "conv_rope_append: rows of %d columns cannot hold %d channels", ld, C);
     const int widest = d > dv ? d : dv;
     FD_REQUIRE(widest <= 256 && n_q + 2 * n_kv <= 65535, -2, "conv_rope_append: heads of %d channels (max 256)", widest);
@@ -289,19 +325,21 @@ extern "C" int fd_conv_rope_append(const void* proj, int ld, int dtype, const fl
     const int threads = (widest / 2 + 31) / 32 * 32;
     const int tpc = T > 64 ? CONV_TPC : 1;        // tokens a CTA takes
     const size_t smem = (size_t)tpc * widest * sizeof(float);
-    const dim3 grid((T + tpc - 1) / tpc, n_q + 2 * n_kv);
+    const dim3 grid((T + tpc - 1) / tpc, n_q + (v_from_k ? 1 : 2) * n_kv);
     if (dtype == 0) {
         auto k = conv_rope_append_kernel<float>;
         return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const float*)proj, ld,
                       conv_w, state, (float*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                       row_q_len, (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q,
-                      n_kv, d, dv, taps, write_kv, update_state, status, T, tpc, interleaved);
+                      n_kv, d, dv, taps, write_kv, update_state, status, T, tpc, interleaved, q_norm_w, k_norm_w, norm_eps,
+                      norm_count, v_from_k);
     }
     auto k = conv_rope_append_kernel<bf16>;
     return launch("conv_rope_append", k, grid, dim3(threads), smem, stream, dim3(1, 1, 1), (const bf16*)proj, ld,
                   conv_w, state, (bf16*)q_out, cos_t, sin_t, table_len, rot, tok_row, tok_pos, row_slot, row_q_start,
                   row_q_len, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv,
-                  d, dv, taps, write_kv, update_state, status, T, tpc, interleaved);
+                  d, dv, taps, write_kv, update_state, status, T, tpc, interleaved, q_norm_w, k_norm_w, norm_eps, norm_count,
+                  v_from_k);
 }
 
 extern "C" int fd_conv_state_update(const void* proj, int ld, int dtype, float* state, const int* row_slot,

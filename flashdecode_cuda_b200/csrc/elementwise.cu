@@ -8,11 +8,11 @@
 namespace fd {
 
 // ---------------------------------------------------------------------------
-// embedding: resid[t, c, :] = float(table[token[t], :]) for each of the `copies` lanes c of the residual stream
+// embedding: resid[t, c, :] = float(table[token[t], :]) * scale for each of the `copies` lanes c of the residual stream
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ resid, int H, int V, int copies, int* status) {
+                             float* __restrict__ resid, int H, int V, int copies, float scale, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -25,14 +25,14 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
     }
     const TW* src = table + (size_t)id * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = to_float(src[i]);
+        const float v = to_float(src[i]) * scale;
         for (int c = 0; c < copies; ++c) dst[(size_t)c * H + i] = v;
     }
 }
 
 // ---------------------------------------------------------------------------
 // residual add + RMSNorm.  For output row j (source row r = rows ? rows[j] : j):
-//   x = resid[r] + sum_p delta[p][r]        (float; parts added in index order)
+//   x = resid[r] + sum_p dscale * delta[p][r]   (float; parts added in index order; dscale 1: a plain sum)
 //   resid[r] = x                             (if write_resid)
 //   out[j] = x * rsqrt(mean(x^2) + eps) * w  (float, rounded once)
 // `delta` may be null (plain norm).  Several parts are the partial sums a
@@ -42,7 +42,7 @@ template <typename TD, typename TW, typename TO>
 __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, size_t part_stride,
                                    float* __restrict__ resid, int write_resid,
                                    const TW* __restrict__ w, float eps, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int H) {
+                                   const int* __restrict__ rows, int H, float dscale) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float smem[];
@@ -55,7 +55,7 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, si
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float x = rrow[i];
         if (delta != nullptr) {
-            for (int p = 0; p < n_parts; ++p) x += to_float(delta[p * part_stride + (size_t)r * H + i]);
+            for (int p = 0; p < n_parts; ++p) x = fmaf(dscale, to_float(delta[p * part_stride + (size_t)r * H + i]), x);
             if (write_resid) rrow[i] = x;
         }
         xs[i] = x;
@@ -75,7 +75,7 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, si
 template <typename TW>
 __global__ void add_rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ delta, float* __restrict__ resid,
                                        int write_resid, const TW* __restrict__ w, float eps,
-                                       __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H) {
+                                       __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H, float dscale) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
@@ -102,7 +102,7 @@ __global__ void add_rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ delta, 
             const uint4 dr = *reinterpret_cast<const uint4*>(delta + (size_t)r * H + i);
             const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dr);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { x[2 * e] += __low2float(d2[e]); x[2 * e + 1] += __high2float(d2[e]); }
+            for (int e = 0; e < 4; ++e) { x[2 * e] = fmaf(dscale, __low2float(d2[e]), x[2 * e]); x[2 * e + 1] = fmaf(dscale, __high2float(d2[e]), x[2 * e + 1]); }
             if (write_resid) {
                 *reinterpret_cast<float4*>(rrow) = make_float4(x[0], x[1], x[2], x[3]);
                 *reinterpret_cast<float4*>(rrow + 4) = make_float4(x[4], x[5], x[6], x[7]);
@@ -130,7 +130,7 @@ template <typename TW, int MAXP>
 __global__ void __launch_bounds__(MAXP > 4 ? 512 : 1024)
 add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride,
                                              float* __restrict__ resid, int write_resid, const TW* __restrict__ w, float eps,
-                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H) {
+                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H, float dscale) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
@@ -165,8 +165,10 @@ add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_
 #pragma unroll
         for (int pt = 0; pt < MAXP; ++pt)
             if (pt < n_parts) {
-                x[0] += d[pt][0].x; x[1] += d[pt][0].y; x[2] += d[pt][0].z; x[3] += d[pt][0].w;
-                x[4] += d[pt][1].x; x[5] += d[pt][1].y; x[6] += d[pt][1].z; x[7] += d[pt][1].w;
+                x[0] = fmaf(dscale, d[pt][0].x, x[0]); x[1] = fmaf(dscale, d[pt][0].y, x[1]);
+                x[2] = fmaf(dscale, d[pt][0].z, x[2]); x[3] = fmaf(dscale, d[pt][0].w, x[3]);
+                x[4] = fmaf(dscale, d[pt][1].x, x[4]); x[5] = fmaf(dscale, d[pt][1].y, x[5]);
+                x[6] = fmaf(dscale, d[pt][1].z, x[6]); x[7] = fmaf(dscale, d[pt][1].w, x[7]);
             }
         if (write_resid) {
             *reinterpret_cast<float4*>(rrow) = make_float4(x[0], x[1], x[2], x[3]);
@@ -334,21 +336,21 @@ using namespace fd;
 typedef __nv_bfloat16 bf16;
 
 extern "C" int fd_embed(const int* tokens, const void* table, int table_dtype, float* resid,
-                        int T, int H, int V, int copies, int* status, cudaStream_t stream) {
+                        int T, int H, int V, int copies, float scale, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(H > 0 && V > 0 && copies >= 1, -2, "embed: bad sizes H=%d V=%d copies=%d", H, V, copies);
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == 0)
         return launch("embed", embed_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
-                      (const float*)table, resid, H, V, copies, status);
+                      (const float*)table, resid, H, V, copies, scale, status);
     return launch("embed", embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
-                  (const bf16*)table, resid, H, V, copies, status);
+                  (const bf16*)table, resid, H, V, copies, scale, status);
 }
 
 template <typename TD, typename TO>
 static int launch_norm(const void* delta, int n_parts, size_t part_stride, float* resid, int write_resid,
                        const void* w, int w_dtype, float eps, void* out, const int* rows, int n_out, int H,
-                       cudaStream_t stream) {
+                       float dscale, cudaStream_t stream) {
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const size_t smem = (((H + 3) & ~3) + 40) * sizeof(float);
     FD_REQUIRE(smem <= 200 * 1024, -2, "add_rmsnorm: width %d needs %zu bytes of shared memory (max 200 KB)", H, smem);
@@ -356,19 +358,19 @@ static int launch_norm(const void* delta, int n_parts, size_t part_stride, float
         auto k = add_rmsnorm_kernel<TD, float, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return launch("add_rmsnorm", k, dim3(n_out), dim3(threads), smem, stream, dim3(1, 1, 1), (const TD*)delta, n_parts,
-                      part_stride, resid, write_resid, (const float*)w, eps, (TO*)out, rows, H);
+                      part_stride, resid, write_resid, (const float*)w, eps, (TO*)out, rows, H, dscale);
     } else {
         auto k = add_rmsnorm_kernel<TD, bf16, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return launch("add_rmsnorm", k, dim3(n_out), dim3(threads), smem, stream, dim3(1, 1, 1), (const TD*)delta, n_parts,
-                      part_stride, resid, write_resid, (const bf16*)w, eps, (TO*)out, rows, H);
+                      part_stride, resid, write_resid, (const bf16*)w, eps, (TO*)out, rows, H, dscale);
     }
 }
 
-// delta_dtype / w_dtype / out_dtype: 0 = float32, 1 = bfloat16.
+// delta_dtype / w_dtype / out_dtype: 0 = float32, 1 = bfloat16.  dscale: what delta is multiplied by as it is added.
 extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, long long part_stride,
                               float* resid, int write_resid, const void* weight, int w_dtype, float eps,
-                              void* out, int out_dtype, const int* rows, int n_out, int H,
+                              void* out, int out_dtype, const int* rows, int n_out, int H, float dscale,
                               cudaStream_t stream) {
     if (n_out == 0) return 0;
     FD_REQUIRE(H > 0, -2, "add_rmsnorm: bad width %d", H);
@@ -380,9 +382,9 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
         const int threads = ((H / 8 + 31) / 32) * 32;
         if (w_dtype == 0)
             return launch("add_rmsnorm", add_rmsnorm_row_kernel<float>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                          (const bf16*)delta, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+                          (const bf16*)delta, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H, dscale);
         return launch("add_rmsnorm", add_rmsnorm_row_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                      (const bf16*)delta, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+                      (const bf16*)delta, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H, dscale);
     }
     if (out_dtype == 1 && delta != nullptr && delta_dtype == 0 && (n_parts <= 4 || (n_parts <= 8 && H <= 4096)) && H % 8 == 0 &&
         H <= 8192 && ps % 4 == 0 &&
@@ -391,22 +393,22 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
         if (n_parts <= 4) {
             if (w_dtype == 0)
                 return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float, 4>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                              (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+                              (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H, dscale);
             return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16, 4>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                          (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+                          (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H, dscale);
         }
         if (w_dtype == 0)
             return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float, 8>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                          (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+                          (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H, dscale);
         return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16, 8>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
-                      (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+                      (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H, dscale);
     }
     if (delta_dtype == 0 && out_dtype == 0)
-        return launch_norm<float, float>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+        return launch_norm<float, float>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, dscale, stream);
     if (delta_dtype == 1 && out_dtype == 1)
-        return launch_norm<bf16, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+        return launch_norm<bf16, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, dscale, stream);
     if (delta_dtype == 0 && out_dtype == 1)
-        return launch_norm<float, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+        return launch_norm<float, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, dscale, stream);
     return fail(-2, "add_rmsnorm: unsupported dtypes delta=%d out=%d", delta_dtype, out_dtype);
 }
 

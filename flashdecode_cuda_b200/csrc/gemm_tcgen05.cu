@@ -773,7 +773,7 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
 // mode 5: out bf16 [M, N] = max(x w_e^T, 0)^2; mode 1: out bf16 [M, N]; mode 2: out float [M, N].  N >= 256 (the
 // persistent kernel).
 // mode 7: every matrix's rows in tiles of 8 gate + 8 up rows, out bf16 [M, N / 2] = the clamped swish of gate times
-// (up + 1) with `limit` (gated_value, act 2).
+// (up + 1) with `limit` (gated_value, act 2); mode 8: the same layout with SiLU(gate) * up; mode 9: tanh-GELU(gate) * up.
 extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int mode, int M, int N, int K, int E,
                                   const int* tile_expert, const int* n_row_tiles, float limit, int* status,
                                   cudaStream_t stream) {
@@ -781,6 +781,8 @@ extern "C" int fd_gemm_tc_grouped(const void* x, const void* w, void* out, int m
     FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     int act = 0;
     if (mode == 7) { mode = 3; act = 2; }
+    else if (mode == 8) { mode = 3; act = 0; }
+    else if (mode == 9) { mode = 3; act = 1; }
     FD_REQUIRE(mode == 5 || mode == 2 || mode == 1 || (mode == 3 && N % 32 == 0), -2,
                "gemm_tcgen05 (grouped): mode %d (the gated form needs N, twice the outputs, to be a multiple of 32)", mode);
     FD_REQUIRE(M % TC_BM == 0 && N >= TW_BN && g_tc_wide != 0 && g_tc_wide != 2, -2,

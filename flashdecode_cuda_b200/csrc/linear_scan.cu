@@ -6,6 +6,9 @@
 //    the first `rot` dimensions of a head at the token's position, dimension i paired with i + rot/2.
 //  * mode 1 (forget gate): a_t = f_t = lower + (1 - lower) * sigmoid(z_t) per channel, b_t = 1 - f_t,
 //    q_t = silu(zq_t); z and zq are columns of the projection.
+//  * mode 2 (decay per key channel): a_t = sigmoid(z_t)^(1/tau) per channel with z a float array of its own (the output
+//    of a product of its own), b_t = k_t, q_t = q_t * q_scale.  The power is taken as exp(log sigmoid(z) / tau) with
+//    log sigmoid(z) = -log(1 + e^-z) worked out on the side where the exponential cannot overflow.
 //
 // The state lives in float per cache slot and is carried from step to step; a step's tokens of a sequence are walked in
 // order, so the sums of every state element are the same whether a prompt comes whole, in portions or token by token.
@@ -46,6 +49,8 @@ struct ScanParams {
     float* out;                        // [T, H * dv]
     const float* decay;                // [H] (mode 0)
     const float* lower;                // [H * d] (mode 1)
+    const float* gate; int gate_ld;    // [T, gate_ld] from the first of the H * d columns on (mode 2)
+    float q_scale, inv_tau;            // (mode 2)
     const float* cos_t; const float* sin_t; int table_len, rot;
     float k_scale;
     const int* row_slot; const int* row_q_start; const int* row_q_len; const int* row_ctx_len;
@@ -104,6 +109,8 @@ __device__ __forceinline__ void stage_tokens(const ScanParams& p, int h, int tok
                 }
             } else if (p.mode == 1) {
                 cc[u] = p.lower[h * d + i];
+            } else if (p.mode == 2) {
+                cc[u] = p.gate[(size_t)(tok0 + tt) * p.gate_ld + h * d + i];
             }
         }
 #pragma unroll
@@ -114,10 +121,16 @@ __device__ __forceinline__ void stage_tokens(const ScanParams& p, int h, int tok
             float* at = dst + tt * tok_stride + chan_at<NR>(i);
             if (i >= d) {
                 at[0] = 0.f; at[CS] = 0.f;
-                if (p.mode == 1) at[2 * CS] = 0.f;
+                if (p.mode != 0) at[2 * CS] = 0.f;
             } else if (p.mode == 0) {
                 at[0] = xq[u] * cc[u] + yq[u] * ss[u];              // first half: x c - y s; second half: x c + y s
                 at[CS] = (xk[u] * cc[u] + yk[u] * ss[u]) * p.k_scale;
+            } else if (p.mode == 2) {
+                const float z = cc[u];
+                const float log_sig = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+                at[0] = xq[u] * p.q_scale;
+                at[CS] = xk[u];
+                at[2 * CS] = expf(log_sig * p.inv_tau);
             } else {
                 const float lo = cc[u];
                 const float f = lo + (1.f - lo) / (1.f + expf(-xk[u]));
@@ -258,7 +271,7 @@ linear_scan_kernel(const ScanParams p) {
             for (int j = 0; j < NR / 4; ++j) {
                 const float4 b4 = br[j];
                 float4 a4 = make_float4(g, g, g, g), q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.mode == 1) a4 = ar[j];
+                if (p.mode != 0) a4 = ar[j];
                 if (PHASE != 1) q4 = qr[j];
                 const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
@@ -269,7 +282,7 @@ linear_scan_kernel(const ScanParams p) {
                     Sr[2] = fmaf(aa[e], Sr[2], bb[e] * vv.z);
                     Sr[3] = fmaf(aa[e], Sr[3], bb[e] * vv.w);
                     if (PHASE == 1) {
-                        if (p.mode == 1) A[4 * j + e] *= aa[e];
+                        if (p.mode != 0) A[4 * j + e] *= aa[e];
                     } else {
                         o[0] = fmaf(Sr[0], qq[e], o[0]);
                         o[1] = fmaf(Sr[1], qq[e], o[1]);
@@ -303,7 +316,7 @@ linear_scan_kernel(const ScanParams p) {
 #pragma unroll
             for (int c = 0; c < SCAN_COLS; ++c)
                 if (v0 + c < dv) u[(size_t)i * dv + v0 + c] = S[ii][c];
-            if (p.mode == 1 && tile == 0 && vl == 0) a[i] = A[ii];
+            if (p.mode != 0 && tile == 0 && vl == 0) a[i] = A[ii];
         }
         return;
     }
@@ -436,6 +449,7 @@ extern "C" long long fd_linear_scan_scratch_floats(int T, int n_rows, int H, int
 // proj [T, ld] of `dtype` (0 float32, 1 bfloat16) holds q at q_col, k (mode 0) or the gate's pre-activation (mode 1)
 // at k_col - H * d columns each - and v at v_col (H * dv columns).  state [slots, H, d, dv] and out [T, H * dv] float.
 // mode 0: decay [H], cos_t / sin_t [table_len, rot / 2] (unused when rot == 0), k_scale.  mode 1: lower [H * d].
+// mode 2: gate [T, gate_ld] float (the decay's pre-activation, H * d columns from the pointer on), q_scale, inv_tau.
 // max_q_len: the longest portion of the step; with scratch memory (fd_linear_scan_scratch_floats floats for the step's T
 // tokens) portions longer than two segments run in segments side by side, otherwise each in one CTA per head and tile.
 extern "C" int fd_linear_scan(const void* proj, int ld, int dtype, int q_col, int k_col, int v_col, float* state,
@@ -443,18 +457,21 @@ extern "C" int fd_linear_scan(const void* proj, int ld, int dtype, int q_col, in
                               const float* sin_t, int table_len, int rot, float k_scale, const int* row_slot,
                               const int* row_q_start, const int* row_q_len, const int* row_ctx_len, int n_rows, int H,
                               int d, int dv, int write_state, int* status, int T, int max_q_len, float* scratch,
-                              long long scratch_floats, cudaStream_t stream) {
+                              long long scratch_floats, const float* gate, int gate_ld, float q_scale, float inv_tau,
+                              cudaStream_t stream) {
     if (n_rows == 0) return 0;
     FD_REQUIRE(H > 0 && d > 0 && dv > 0 && d <= 256, -2, "linear_scan: %d heads of %d x %d (d at most 256)", H, d, dv);
-    FD_REQUIRE(mode == 0 || mode == 1, -2, "linear_scan: unknown mode %d", mode);
-    FD_REQUIRE(mode == 1 ? lower != nullptr : decay != nullptr, -2, "linear_scan: the mode's constants are missing");
-    FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d && (rot == 0 || mode == 1 || (cos_t && sin_t)), -2,
+    FD_REQUIRE(mode >= 0 && mode <= 2, -2, "linear_scan: unknown mode %d", mode);
+    FD_REQUIRE(mode == 1 ? lower != nullptr : (mode == 2 ? gate != nullptr && gate_ld >= H * d : decay != nullptr), -2,
+               "linear_scan: the mode's constants are missing");
+    FD_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d && (rot == 0 || mode != 0 || (cos_t && sin_t)), -2,
                "linear_scan: %d rotated dimensions of %d", rot, d);
     FD_REQUIRE(H <= 65535, -2, "linear_scan: %d heads", H);
     ScanParams p;
     p.proj = proj; p.ld = ld; p.q_col = q_col; p.k_col = k_col; p.v_col = v_col; p.state = state; p.out = out;
     p.decay = decay; p.lower = lower; p.cos_t = cos_t; p.sin_t = sin_t; p.table_len = table_len;
     p.rot = mode == 0 ? rot : 0; p.k_scale = k_scale;
+    p.gate = gate; p.gate_ld = gate_ld; p.q_scale = q_scale; p.inv_tau = inv_tau;
     p.row_slot = row_slot; p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len;
     p.H = H; p.d = d; p.dv = dv; p.mode = mode; p.write_state = write_state; p.status = status;
     p.DS = scan_ds(d);

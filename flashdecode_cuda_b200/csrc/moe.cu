@@ -1,8 +1,11 @@
 // Routed feed-forward (mixture of experts), all decisions on the device:
 //
 //  * moe_route: per token, router logits in float (one output per warp pass, k in
-//    lane order), softmax over all router outputs, the `top` largest of score +
-//    correction (ties: the lower index), and the chosen scores over their sum;
+//    lane order), scores = softmax over all router outputs or a sigmoid of each,
+//    the `top` largest of score + correction (ties: the lower index) - by option
+//    only among the best groups of neighbouring outputs, a group ranking by the
+//    sum of its two largest score + correction - and as weights the chosen
+//    scores over their sum, or the chosen scores times a constant;
 //  * moe_align: the (token, choice) pairs that go to an expert with weights,
 //    grouped by expert, each group padded to whole row tiles, with the expert of
 //    every tile and the number of tiles;
@@ -37,10 +40,13 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ logits,
                  const float* __restrict__ correction, const float* __restrict__ bias, int* __restrict__ ids,
-                 float* __restrict__ wts, int H, int n_out, int top) {
-    extern __shared__ __align__(16) float z_s[];         // [n_out] logits, then scores; [n_out] choice scores; [H] the row
+                 float* __restrict__ wts, int H, int n_out, int top, int sigmoid_scores, int n_groups, int keep_groups,
+                 int renorm, float weight_scale) {
+    // [n_out] logits, then scores; [n_out] choice scores; [n_groups] the groups' ranks; [H] the row
+    extern __shared__ __align__(16) float z_s[];
     float* c_s = z_s + n_out;
-    float* x_s = c_s + n_out;
+    float* g_s = c_s + n_out;
+    float* x_s = g_s + ((n_groups + 3) & ~3);
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (logits != nullptr) {
@@ -72,22 +78,52 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* 
     }
     __syncthreads();
     if (warp != 0) return;
-    float m = -INFINITY;
-    for (int o = lane; o < n_out; o += 32) m = fmaxf(m, z_s[o]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int o = lane; o < n_out; o += 32) {
-        const float e = expf(z_s[o] - m);
-        z_s[o] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    for (int o = lane; o < n_out; o += 32) {
-        const float s = z_s[o] / sum;
-        z_s[o] = s;
-        c_s[o] = s + (correction != nullptr ? correction[o] : 0.f);
+    if (sigmoid_scores) {
+        for (int o = lane; o < n_out; o += 32) {
+            const float s = 1.f / (1.f + expf(-z_s[o]));
+            z_s[o] = s;
+            c_s[o] = s + (correction != nullptr ? correction[o] : 0.f);
+        }
+    } else {
+        float m = -INFINITY;
+        for (int o = lane; o < n_out; o += 32) m = fmaxf(m, z_s[o]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int o = lane; o < n_out; o += 32) {
+            const float e = expf(z_s[o] - m);
+            z_s[o] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        for (int o = lane; o < n_out; o += 32) {
+            const float s = z_s[o] / sum;
+            z_s[o] = s;
+            c_s[o] = s + (correction != nullptr ? correction[o] : 0.f);
+        }
     }
     __syncwarp();
+    if (n_groups > 1 && keep_groups < n_groups) {
+        // a group's rank: the sum of its two largest choice scores (of its one, if it has one member); outputs of groups
+        // outside the best `keep_groups` (ties: the lower group) cannot be chosen
+        const int per = n_out / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;
+            for (int o = g * per; o < (g + 1) * per; ++o) {
+                const float v = c_s[o];
+                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+            }
+            g_s[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        for (int g = lane; g < n_groups; g += 32) {
+            const float mine = g_s[g];
+            int ahead = 0;
+            for (int o = 0; o < n_groups; ++o) ahead += (g_s[o] > mine) || (g_s[o] == mine && o < g);
+            if (ahead >= keep_groups)
+                for (int o = g * per; o < (g + 1) * per; ++o) c_s[o] = -INFINITY;
+        }
+        __syncwarp();
+    }
     float chosen_sum = 0.f;
     for (int c = 0; c < top; ++c) {
         float best = -INFINITY;
@@ -110,7 +146,7 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* 
         chosen_sum += z_s[bi];
         __syncwarp();
     }
-    const float inv = 1.f / (chosen_sum + 1e-20f);
+    const float inv = renorm ? 1.f / (chosen_sum + 1e-20f) : weight_scale;
     for (int c = lane; c < top; c += 32) wts[(size_t)t * top + c] = z_s[ids[(size_t)t * top + c]] * inv;
 }
 
@@ -162,12 +198,12 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int*
 // MODE 1: a[row] = act[row],                  out = acc as T into y [cap, N]
 // MODE 2: a[row] = x[sorted_pair[row] / top], out = acc as T into [cap, N] (an activation kernel follows)
 // MODE 3: a[row] = x[sorted_pair[row] / top], w rows in tiles of 8 gate + 8 up rows, out [cap, N / 2] =
-//         gated_value(act 2: clamped swish with `limit`) of each gate / up pair
+//         gated_value(act; 2 = clamped swish with `limit`) of each gate / up pair
 template <typename T, int MODE>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restrict__ out,
                 const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
-                const int* __restrict__ n_tiles, int top, int N, int K, float limit) {
+                const int* __restrict__ n_tiles, int top, int N, int K, float limit, int act) {
     const int tile = blockIdx.y;
     if (tile >= *n_tiles) return;
     __shared__ float a_s[MOE_MT][MOE_KT + 1];
@@ -217,7 +253,7 @@ moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, void* __restri
                 const int r = 2 * ty + i, c = n0 + 16 * j + tx;
                 if (tx < 8 && row_s[r] >= 0 && c + 8 < N)
                     static_cast<T*>(out)[(size_t)(tile * MOE_MT + r) * (N >> 1) + ((n0 + 16 * j) >> 1) + tx] =
-                        from_float<T>(gated_value(2, acc[i][j], other, limit));
+                        from_float<T>(gated_value(act, acc[i][j], other, limit));
             }
         return;
     }
@@ -247,7 +283,7 @@ template <int BM, int BN, int WM, int WN, int MODE>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
-                    const int* __restrict__ n_tiles, int top, int N, int K, float limit) {
+                    const int* __restrict__ n_tiles, int top, int N, int K, float limit, int act) {
     constexpr int THREADS = WM * WN * 32, BK = 64, STAGES = 3;
     constexpr int TM = BM / WM, TN = BN / WN, MI = TM / 16, NI = TN / 8;
     static_assert(TM % 16 == 0 && TN % 16 == 0, "a warp takes whole 16 x 16 parts");
@@ -338,8 +374,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
                     const int cg = n0 + wn * TN + j * 8;
                     if (cg + 16 > N) continue;
                     *reinterpret_cast<__nv_bfloat162*>(o + (cg >> 1) + (lane & 3) * 2) =
-                        __floats2bfloat162_rn(gated_value(2, acc[i][j][hh * 2], acc[i][j + 1][hh * 2], limit),
-                                              gated_value(2, acc[i][j][hh * 2 + 1], acc[i][j + 1][hh * 2 + 1], limit));
+                        __floats2bfloat162_rn(gated_value(act, acc[i][j][hh * 2], acc[i][j + 1][hh * 2], limit),
+                                              gated_value(act, acc[i][j][hh * 2 + 1], acc[i][j + 1][hh * 2 + 1], limit));
                 }
                 continue;
             }
@@ -363,7 +399,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
 
 template <int BM, int BN, int WM, int WN, int MODE>
 static int launch_moe_mma(const void* a, const void* w, void* out, const int* sorted_pair, const int* tile_expert,
-                          const int* n_tiles, int cap, int top, int N, int K, float limit, cudaStream_t stream) {
+                          const int* n_tiles, int cap, int top, int N, int K, float limit, int act, cudaStream_t stream) {
     auto k = moe_gemm_mma_kernel<BM, BN, WM, WN, MODE>;
     const size_t smem = (size_t)3 * (BM + BN) * 64 * 2 + BM * sizeof(int);
     static bool configured = false;
@@ -375,7 +411,7 @@ static int launch_moe_mma(const void* a, const void* w, void* out, const int* so
     dim3 grid((N + BN - 1) / BN, cap / BM);
     FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
     return launch("moe_gemm", k, grid, dim3(WM * WN * 32), smem, stream, dim3(1, 1, 1), (const __nv_bfloat16*)a,
-                  (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit);
+                  (const __nv_bfloat16*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit, act);
 }
 
 // xs[row] = x[sorted_pair[row] / top] for the grouped rows that exist, zeros for the padding rows among them: the
@@ -471,19 +507,25 @@ extern "C" int fd_moe_tile_rows(int dtype, int rows_per_expert) { return dtype =
 // bias [n_out] float or null: added to the logits before the softmax (correction only shifts the choice).
 extern "C" int fd_moe_route(const void* x, const void* w, int dtype, const float* logits, const float* correction,
                             const float* bias, int* ids, float* wts, int T, int H, int n_out, int top,
+                            int sigmoid_scores, int n_groups, int keep_groups, int renorm, float weight_scale,
                             cudaStream_t stream) {
     if (T == 0) return 0;
+    FD_REQUIRE(n_groups >= 1 && n_out % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+               (long long)keep_groups * (n_out / n_groups) >= top, -2,
+               "moe_route: %d of %d groups of %d router outputs for %d choices", keep_groups, n_groups, n_out, top);
     FD_REQUIRE(n_out >= 1 && top >= 1 && top <= n_out && n_out <= 4096, -2,
                "moe_route: %d choices of %d router outputs (at most 4096)", top, n_out);
-    const size_t smem = (2 * (size_t)n_out + (logits ? 0 : H)) * sizeof(float);
+    const size_t smem = (2 * (size_t)n_out + ((n_groups + 3) & ~3) + (logits ? 0 : H)) * sizeof(float);
     FD_REQUIRE(smem <= 48 * 1024, -2, "moe_route: a row of %d and %d outputs need %zu bytes of shared memory (max 48 KB); "
                "give the logits", H, n_out, smem);
     const int threads = logits != nullptr ? 32 : (n_out >= 32 ? ROUTE_THREADS : ((n_out + 7) / 8 * 8) * 32);
     if (dtype == 0)
         return launch("moe_route", moe_route_kernel<float>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
-                      (const float*)x, (const float*)w, logits, correction, bias, ids, wts, H, n_out, top);
+                      (const float*)x, (const float*)w, logits, correction, bias, ids, wts, H, n_out, top, sigmoid_scores,
+                      n_groups, keep_groups, renorm, weight_scale);
     return launch("moe_route", moe_route_kernel<bf16>, dim3(T), dim3(threads), smem, stream, dim3(1, 1, 1),
-                  (const bf16*)x, (const bf16*)w, logits, correction, bias, ids, wts, H, n_out, top);
+                  (const bf16*)x, (const bf16*)w, logits, correction, bias, ids, wts, H, n_out, top, sigmoid_scores, n_groups,
+                  keep_groups, renorm, weight_scale);
 }
 
 // cap: rows of the grouped buffers, at least P rounded up to whole tiles plus one tile per expert.
@@ -503,25 +545,27 @@ extern "C" int fd_moe_align(const int* ids, int P, int E, int* pair_pos, int* so
 // mode 2: a = x [T, K], out [cap, N] (dtype) = x W_e^T.
 // w [E, N, K].
 // mt: the tile rows the grouping was made with.
-// mode 3: a = x [T, K], w rows in tiles of 8 gate + 8 up, out [cap, N / 2] = clamped swish of gate times (up + 1).
+// mode 3: a = x [T, K], w rows in tiles of 8 gate + 8 up, out [cap, N / 2] = gated_value(act) of each gate / up pair:
+// act 0 SiLU(gate) up, 1 tanh-GELU(gate) up, 2 clamped swish of gate times (up + 1) with `limit`.
 extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, int mode, const int* sorted_pair,
                            const int* tile_expert, const int* n_tiles, int cap, int mt, int top, int N, int K,
-                           float limit, cudaStream_t stream) {
+                           float limit, int act, cudaStream_t stream) {
     if (cap == 0) return 0;
+    FD_REQUIRE(act >= 0 && act <= 2, -2, "moe_gemm: unknown gated activation %d", act);
     FD_REQUIRE(cap % mt == 0 && N > 0 && K > 0 && mode >= 0 && mode <= 3 && (mode != 3 || N % 16 == 0), -2,
                "moe_gemm: bad sizes or mode (the gated form needs N, twice the outputs, to be a multiple of 16)");
     if (dtype == 1 && K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0) {
         if (mt == 128) {
-            if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            if (mode == 2) return launch_moe_mma<128, 128, 2, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            if (mode == 3) return launch_moe_mma<128, 128, 2, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 0) return launch_moe_mma<128, 128, 2, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            if (mode == 2) return launch_moe_mma<128, 128, 2, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            if (mode == 3) return launch_moe_mma<128, 128, 2, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            return launch_moe_mma<128, 128, 2, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
         }
         if (mt == 32) {
-            if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            if (mode == 2) return launch_moe_mma<32, 64, 1, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            if (mode == 3) return launch_moe_mma<32, 64, 1, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
-            return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, stream);
+            if (mode == 0) return launch_moe_mma<32, 64, 1, 4, 0>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            if (mode == 2) return launch_moe_mma<32, 64, 1, 4, 2>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            if (mode == 3) return launch_moe_mma<32, 64, 1, 4, 3>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
+            return launch_moe_mma<32, 64, 1, 4, 1>(a, w, out, sorted_pair, tile_expert, n_tiles, cap, top, N, K, limit, act, stream);
         }
     }
     FD_REQUIRE(mt == MOE_MT, -2, "moe_gemm: the CUDA-core product takes tiles of %d rows, not %d", MOE_MT, mt);
@@ -529,7 +573,7 @@ extern "C" int fd_moe_gemm(const void* a, const void* w, void* out, int dtype, i
     FD_REQUIRE(grid.y <= 65535, -2, "moe_gemm: %d row tiles are too many", (int)grid.y);
 #define FD_MG(T_, M_)                                                                                                \
     return launch("moe_gemm", moe_gemm_kernel<T_, M_>, grid, dim3(MOE_THREADS), 0, stream, dim3(1, 1, 1), (const T_*)a, \
-                  (const T_*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit)
+                  (const T_*)w, out, sorted_pair, tile_expert, n_tiles, top, N, K, limit, act)
     if (dtype == 0) { if (mode == 0) FD_MG(float, 0); if (mode == 2) FD_MG(float, 2); if (mode == 3) FD_MG(float, 3); FD_MG(float, 1); }
     if (mode == 0) FD_MG(bf16, 0);
     if (mode == 2) FD_MG(bf16, 2);

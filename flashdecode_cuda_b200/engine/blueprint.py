@@ -69,10 +69,13 @@ class RunSpec:
     weights are shared, its cache is not).  ``cache_from``: index of an EARLIER
     entry whose keys/values and state this entry reads instead of keeping its
     own.  ``before``: name of a stream operation (``ModelBlueprint.stream_ops``)
-    that rewrites the residual stream right before this entry's layer runs."""
+    that rewrites the residual stream right before this entry's layer runs;
+    ``before_index``: a number handed to that operation (which pass of a loop
+    starts here)."""
     layer: int
     cache_from: Optional[int] = None
     before: Optional[str] = None
+    before_index: Optional[int] = None
 
 
 @dataclass
@@ -91,6 +94,8 @@ class ModelBlueprint:
     # lanes of the residual stream: the step's stream is [T, lanes * hidden_size] float32, every lane equal to the
     # embedding output at the start; the blocks and the final norm of such a model are the ones that know lanes
     lanes: int = 1
+    # lookup tables that several parts read by token id, by the name those parts ask for (``table="name"``)
+    tables: Dict[str, PartSpec] = field(default_factory=dict)
 
     def validate(self) -> None:
         if self.lanes < 1 or (self.lanes > 1 and self.stream_ops):

@@ -139,6 +139,7 @@ class Model:
         self.hidden_size = blueprint.hidden_size
         self.vocab_size = blueprint.vocab_size
         self.positions = {name: self._build(spec) for name, spec in blueprint.positions.items()}
+        self.tables = {name: self._build(spec) for name, spec in blueprint.tables.items()}
         self.embedding = self._build(blueprint.embedding)
         self.blocks = []
         for ls in blueprint.layers:
@@ -167,6 +168,8 @@ class Model:
         params = dict(spec.params)
         if isinstance(params.get("position"), str):
             params["position"] = self.positions[params["position"]]
+        if isinstance(params.get("table"), str):
+            params["table"] = self.tables[params["table"]]
         for k, v in params.items():          # parts made of parts (mixers side by side): built first, handed over whole
             if isinstance(v, PartSpec):
                 params[k] = self._build(v)
@@ -177,7 +180,7 @@ class Model:
         return cls(prefix=spec.prefix, **params)
 
     def all_parts(self) -> list:
-        parts = list(self.positions.values()) + [self.embedding]
+        parts = list(self.positions.values()) + list(self.tables.values()) + [self.embedding]
         for b in self.blocks:
             parts += [b] + list(b.parts())
         return parts + list(self.stream_ops.values()) + [self.final_norm, self.head]
@@ -394,7 +397,7 @@ class Model:
         if self.trace is not None:
             self.trace["embed"] = resid[:, :self.hidden_size].detach().float().cpu().clone()
         embedded = None
-        if self.stream_ops:
+        if any(getattr(op, "needs_embedded", True) for op in self.stream_ops.values()):
             # stream operations may read the embedding output again later in the step
             embedded = ctx.ws.get("embedded", (ctx.T, self.hidden_size), torch.float32)
             embedded.copy_(resid)
@@ -403,7 +406,10 @@ class Model:
         for i, run in enumerate(self.schedule):
             if run.before is not None:
                 # the operation adds the pending delta itself and leaves the new stream in resid
-                delta = self.stream_ops[run.before].forward(ctx, resid, delta, embedded)
+                if run.before_index is None:
+                    delta = self.stream_ops[run.before].forward(ctx, resid, delta, embedded)
+                else:
+                    delta = self.stream_ops[run.before].forward(ctx, resid, delta, embedded, index=run.before_index)
             # whoever norms next - the next entry's block or the final norm - says whether it takes float
             # partial sums [parts, T, H] for a delta; a block hands that on to its last sub-layer
             last = i + 1 >= len(self.schedule)

@@ -70,8 +70,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_device_arch": [],
         "fd_set_pdl": [I],
         "fd_sm_count": [],
-        "fd_embed": [P, P, I, P, I, I, I, I, P, P],
-        "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, P],
+        "fd_embed": [P, P, I, P, I, I, I, I, F, P, P],
+        "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, F, P],
         "fd_silu_mul": [P, P, I, I, I, I, P],
         "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, c_ulonglong, P],
@@ -96,21 +96,21 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P],
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
-        "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
+        "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P, P, F, I, I, P],
         "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, I, P],
         "fd_attn_head_mix": [P, P, P, I, I, I, I, I, I, F, P],
         "fd_add_dyn_tanh": [P, I, P, I, P, P, F, P, I, P, I, I, P],
         "fd_quad_exp_act": [P, P, I, P, LL, P],
         "fd_scale_f32": [P, LL, F, P],
         "fd_axpy_f32": [P, P, I, LL, F, I, P],
-        "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, I, I, P, LL, P],
+        "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, I, I, P, LL, P, I, F, F, P],
         "fd_head_norm_gate": [P, P, P, I, P, I, I, I, I, I, F, F, P],
         "fd_conv_state_update": [P, I, I, P, P, P, P, I, I, I, P],
         "fd_gate_mul": [P, P, I, P, I, I, I, P],
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
         "fd_relu2": [P, P, I, LL, P],
         "fd_moe_tile_rows": [I, I],
-        "fd_moe_route": [P, P, I, P, P, P, P, P, I, I, I, I, P],
+        "fd_moe_route": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
         "fd_glu_mul": [P, P, I, I, I, I, I, F, P],
         "fd_softcap": [P, LL, F, P],
         "fd_lanes_norm": [P, I, I, LL, P, P, P, P, I, P, P, F, P, I, P, I, I, I, P],
@@ -119,7 +119,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_norm_append": [P, I, P, I, P, P, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, P, P],
         "fd_head_gemm": [P, P, P, I, I, I, I, I, P],
         "fd_moe_align": [P, I, I, P, P, P, P, I, I, P],
-        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, F, P],
+        "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, F, I, P],
+        "fd_add_cast": [P, I, P, P, I, I, I, F, P],
+        "fd_side_gate_mul": [P, P, P, I, I, I, P, I, I, I, P, P],
+        "fd_token_side_row": [P, I, P, F, P, P, I, I, I, P, P, P, I, F, P, I, I, I, I, P, P],
+        "fd_add_row_vector": [P, I, P, P, I, I, F, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
         "fd_moe_gather": [P, P, P, P, I, I, I, I, P],
         "fd_gemm_tc_grouped": [P, P, P, I, I, I, I, I, P, P, F, P, P],
@@ -220,20 +224,21 @@ def status_message(word: int) -> str:
 
 # ---------------------------------------------------------------------------
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
-    """resid[t] = float(table[tokens[t]]); tokens int32 [T], resid float32 [T, H] - or [T, lanes * H], a residual
-    stream of several lanes, every one of which receives the row."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, resid: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
+    """resid[t] = float(table[tokens[t]]) * scale; tokens int32 [T], resid float32 [T, H] - or [T, lanes * H], a
+    residual stream of several lanes, every one of which receives the row."""
     T = tokens.numel()
     V, H = table.shape
     assert tokens.dtype == torch.int32 and resid.dtype == torch.float32 and resid.shape[-1] % H == 0
     _check(lib().fd_embed(_ptr(tokens), _ptr(table), _dt(table.dtype), _ptr(resid), T, H, V, resid.shape[-1] // H,
-                          _ptr(status), _stream()))
+                          float(scale), _ptr(status), _stream()))
 
 
 def add_rmsnorm(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,
-                write_resid: bool = True, n_parts: int = 1) -> None:
-    """out[j] = rmsnorm(resid[r] + delta[r]) * weight with r = rows[j] (or j);
+                write_resid: bool = True, n_parts: int = 1, delta_scale: float = 1.0) -> None:
+    """out[j] = rmsnorm(resid[r] + delta_scale * delta[r]) * weight with r = rows[j] (or j);
     resid[r] takes the sum when ``write_resid``.  ``delta`` None: plain norm.
     ``delta`` [parts, rows, H] (or ``n_parts`` > 1) holds partial sums, added in order."""
     H = resid.shape[-1]
@@ -248,7 +253,7 @@ def add_rmsnorm(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torc
     _check(lib().fd_add_rmsnorm(_ptr(delta), _dt(delta.dtype) if delta is not None else _dt(out.dtype),
                                 n_parts, part_stride, _ptr(resid), int(write_resid), _ptr(weight),
                                 _dt(weight.dtype), float(eps), _ptr(out), _dt(out.dtype), _ptr(rows),
-                                n_out, H, _stream()))
+                                n_out, H, float(delta_scale), _stream()))
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, tiled: bool = False) -> None:
@@ -773,7 +778,7 @@ def axpy_f32(y: torch.Tensor, x: torch.Tensor, s: float, accumulate: bool = True
     _check(lib().fd_axpy_f32(_ptr(y), _ptr(x), _dt(x.dtype), y.numel(), float(s), int(accumulate), _stream()))
 
 
-SCAN_DECAY, SCAN_GATED = 0, 1
+SCAN_DECAY, SCAN_GATED, SCAN_CHANNEL_DECAY = 0, 1, 2
 
 
 def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: torch.Tensor, out: torch.Tensor,
@@ -782,13 +787,15 @@ def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: t
                 write_state: bool, status: torch.Tensor, decay: Optional[torch.Tensor] = None,
                 lower: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
                 sin: Optional[torch.Tensor] = None, rot_dims: int = 0, k_scale: float = 1.0, max_q_len: int = 0,
-                scratch: Optional[torch.Tensor] = None) -> None:
+                scratch: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_col: int = 0,
+                q_scale: float = 1.0, tau: float = 1.0) -> None:
     """The recurrence S_t = diag(a_t) S_(t-1) + b_t v_t^T, o_t = S_t^T q_t per sequence and head over the step's
     tokens, from ``state`` [slots, heads, head_dim, v_head_dim] (float32, updated when ``write_state``) to ``out``
     [T, heads * v_head_dim] (float32).  q, k and v are column ranges of ``proj`` [T, ld].  ``SCAN_DECAY``: a = decay[h],
     b = rotated k times ``k_scale``, q rotated (the first ``rot_dims`` dimensions, i paired with i + rot_dims / 2).
     ``SCAN_GATED``: the k columns hold the gate's pre-activation z; a = lower + (1 - lower) sigmoid(z), b = 1 - a,
-    q = silu of the q columns.  With ``scratch`` (float32, ``linear_scan_scratch_floats`` elements) and ``max_q_len`` (the
+    q = silu of the q columns.  ``SCAN_CHANNEL_DECAY``: a = sigmoid(z)^(1 / tau) per key channel with z the columns
+    ``gate_col ...`` of ``gate`` [T, ldg] (float32), b = the k columns, q = the q columns times ``q_scale``.  With ``scratch`` (float32, ``linear_scan_scratch_floats`` elements) and ``max_q_len`` (the
     longest portion of the step), portions longer than two segments are cut into segments that run side by side."""
     T = proj.shape[0]
     assert state.dtype == out.dtype == torch.float32 and state.shape[1:] == (n_heads, head_dim, v_head_dim)
@@ -798,8 +805,12 @@ def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: t
         assert decay is not None and decay.dtype == torch.float32 and decay.numel() == n_heads
         if rot_dims:
             assert cos.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and sin.shape == cos.shape
-    else:
+    elif mode == SCAN_GATED:
         assert lower is not None and lower.dtype == torch.float32 and lower.numel() == n_heads * head_dim
+        rot_dims = 0
+    else:
+        assert gate is not None and gate.dtype == torch.float32 and gate.shape[0] == T and gate.is_contiguous()
+        assert gate_col + n_heads * head_dim <= gate.shape[1] and tau > 0
         rot_dims = 0
     _check(lib().fd_linear_scan(_ptr(proj), proj.shape[1], _dt(proj.dtype), q_col, k_col, v_col, _ptr(state), _ptr(out),
                                 mode, _ptr(decay), _ptr(lower), _ptr(cos) if rot_dims else None,
@@ -807,7 +818,9 @@ def linear_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, state: t
                                 float(k_scale), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
                                 n_rows, n_heads, head_dim, v_head_dim, int(write_state), _ptr(status), T, int(max_q_len),
                                 _ptr(scratch) if scratch is not None else None,
-                                scratch.numel() if scratch is not None else 0, _stream()))
+                                scratch.numel() if scratch is not None else 0,
+                                _col_ptr(gate, gate_col) if gate is not None else None,
+                                gate.shape[1] if gate is not None else 0, float(q_scale), 1.0 / float(tau), _stream()))
 
 
 def linear_scan_segment() -> int:
@@ -844,7 +857,9 @@ def conv_rope_append(proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[t
                      tok_pos: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int,
                      head_dim: int, v_head_dim: int, write_kv: bool, update_state: bool, status: torch.Tensor,
-                     interleaved: bool = False, first_col: int = 0) -> None:
+                     interleaved: bool = False, first_col: int = 0, q_norm: Optional[torch.Tensor] = None,
+                     k_norm: Optional[torch.Tensor] = None, norm_eps: float = 0.0, norm_count: int = 0,
+                     values_from_keys: bool = False) -> None:
     """For every token: the causal convolution over time of each q, k and v channel of ``proj``
     [T, >= C] (C = (n_q + n_kv) head_dim + n_kv v_head_dim leading columns) with ``conv_w`` [C, taps]
     (float32), earlier steps' values taken from ``state`` [slots, taps - 1, C] (float32); rotation of
@@ -852,10 +867,15 @@ def conv_rope_append(proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[t
     ``q_out`` [T, n_q head_dim], k and v to the paged pools.  ``update_state``: rows that bring one
     token move their state on in the same kernel (use ``conv_state_update`` for the others).
     ``interleaved``: the rotation pairs dimension 2i with 2i + 1.  ``first_col``: the column of ``proj``
-    at which the C channels start (an even number)."""
+    at which the C channels start (an even number).  ``q_norm`` / ``k_norm`` [head_dim] float32: every q / k head is
+    RMS-normed with that weight (``norm_eps``; the mean over ``norm_count`` dimensions, default head_dim) after the
+    convolution and before the rotation.  ``values_from_keys``: ``proj`` has no v columns (C = (n_q + n_kv) head_dim)
+    and the value pool receives the convolved keys as they are before norm and rotation."""
     T = proj.shape[0]
     taps = conv_w.shape[1]
-    C = (n_q + n_kv) * head_dim + n_kv * v_head_dim
+    C = (n_q + n_kv) * head_dim + (0 if values_from_keys else n_kv * v_head_dim)
+    for nw in (q_norm, k_norm):
+        assert nw is None or (nw.dtype == torch.float32 and nw.numel() == head_dim)
     assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and proj.shape[1] >= first_col + C
     assert first_col % 2 == 0 and proj.is_contiguous()
     assert state is None or (state.dtype == torch.float32 and state.shape[1:] == (taps - 1, C))
@@ -871,7 +891,8 @@ def conv_rope_append(proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[t
                                      _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(k_pool), _ptr(v_pool),
                                      _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, n_q, n_kv,
                                      head_dim, v_head_dim, taps, int(write_kv), int(update_state), _ptr(status),
-                                     int(interleaved), _stream()))
+                                     int(interleaved), _ptr(q_norm), _ptr(k_norm), float(norm_eps),
+                                     int(norm_count or head_dim), int(values_from_keys), _stream()))
 
 
 def conv_state_update(proj: torch.Tensor, state: torch.Tensor, row_slot: torch.Tensor, row_q_start: torch.Tensor,
@@ -903,6 +924,50 @@ def add_concat(delta: Optional[torch.Tensor], resid: torch.Tensor, other: torch.
                                _ptr(out), _dt(out.dtype), T, H, _stream()))
 
 
+def add_cast(delta: Optional[torch.Tensor], resid: torch.Tensor, out: torch.Tensor, delta_scale: float = 1.0) -> None:
+    """resid += delta_scale * delta (if given); out [T, H] = resid rounded to out's dtype; resid float32 [T, H]."""
+    T, H = resid.shape
+    assert resid.dtype == torch.float32 and out.shape == (T, H) and (delta is None or delta.shape == (T, H))
+    _check(lib().fd_add_cast(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid), _ptr(out),
+                             _dt(out.dtype), T, H, float(delta_scale), _stream()))
+
+
+def side_gate_mul(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, first_col: int, g: torch.Tensor,
+                  status: torch.Tensor) -> None:
+    """g[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], first_col + j]; z float32 [T, dim], g [T, dim] in the table's
+    dtype."""
+    T, dim = z.shape
+    assert z.dtype == torch.float32 and g.shape == (T, dim) and g.dtype == table.dtype and tokens.dtype == torch.int32
+    _check(lib().fd_side_gate_mul(_ptr(z), _ptr(tokens), _ptr(table), table.shape[1], first_col, table.shape[0], _ptr(g),
+                                  _dt(g.dtype), T, dim, _ptr(status), _stream()))
+
+
+TOKEN_SIDE_ROW_MAX_FLOATS = 12000 - 48      # floats of shared memory the one-launch form has for a row and its gate values
+
+
+def token_side_row(delta: Optional[torch.Tensor], resid: torch.Tensor, delta_scale: float, tokens: torch.Tensor,
+                   table: torch.Tensor, first_col: int, gate_w: torch.Tensor, proj_w: torch.Tensor,
+                   norm_w: torch.Tensor, eps: float, out: torch.Tensor, status: torch.Tensor) -> None:
+    """In one launch, a CTA per token: resid += delta_scale * delta; g = gelu_tanh(gate_w x) * table[token, first_col ...];
+    y = proj_w g; out = y / sqrt(mean(y^2) + eps) * norm_w (float32 [T, H]).  gate_w [dim, H], proj_w [H, dim]."""
+    T, H = resid.shape
+    dim = gate_w.shape[0]
+    assert resid.dtype == out.dtype == torch.float32 and out.shape == (T, H) and gate_w.shape == (dim, H)
+    assert proj_w.shape == (H, dim) and gate_w.dtype == proj_w.dtype == table.dtype and norm_w.numel() == H
+    _check(lib().fd_token_side_row(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid),
+                                   float(delta_scale), _ptr(tokens), _ptr(table), table.shape[1], first_col, table.shape[0],
+                                   _ptr(gate_w), _ptr(proj_w), _ptr(norm_w), _dt(norm_w.dtype), float(eps), _ptr(out),
+                                   _dt(gate_w.dtype), T, H, dim, _ptr(status), _stream()))
+
+
+def add_row_vector(delta: Optional[torch.Tensor], resid: torch.Tensor, vec: torch.Tensor, delta_scale: float = 1.0) -> None:
+    """resid <- resid + delta_scale * delta + vec; resid float32 [T, H], vec float32 [H], delta [T, H] or None."""
+    T, H = resid.shape
+    assert resid.dtype == vec.dtype == torch.float32 and vec.numel() == H and (delta is None or delta.shape == (T, H))
+    _check(lib().fd_add_row_vector(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid), _ptr(vec),
+                                   T, H, float(delta_scale), _stream()))
+
+
 def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
     """out = max(x, 0)^2."""
     assert x.shape == out.shape and x.dtype == out.dtype
@@ -929,13 +994,18 @@ ROUTE_FUSED_MAX_ROW = 8192      # widest row of x the routing kernel takes into 
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
-              wts: torch.Tensor, logits: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
+              wts: torch.Tensor, logits: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+              sigmoid_scores: bool = False, n_groups: int = 1, keep_groups: int = 1,
+              weight_scale: Optional[float] = None) -> None:
     """Per row of x [T, H]: softmax scores over the rows of ``router`` [n_out, H] (float arithmetic), the ``top``
     outputs with the largest score + correction into ``ids`` [T, top] (int32), and their scores over their sum
     (+ 1e-20) into ``wts`` [T, top] (float32).  ``logits`` [T, n_out] float32: the router's outputs made by a matrix
     product beforehand (steps of many tokens); without them the kernel makes them itself, a token per CTA.
     ``bias`` [n_out] float32 is added to the logits before the softmax.  The chosen scores over their sum are the
-    softmax over the chosen logits alone."""
+    softmax over the chosen logits alone.  ``sigmoid_scores``: the scores are sigmoid(logit) instead of the softmax.
+    ``n_groups`` > ``keep_groups``: the outputs form ``n_groups`` equal groups of neighbours, a group ranks by the sum of
+    its two largest score + correction, and only outputs of the best ``keep_groups`` groups can be chosen.
+    ``weight_scale``: the weights are the chosen scores times this constant, not divided by their sum."""
     T, H = x.shape
     n_out, top = router.shape[0], ids.shape[1]
     assert router.shape == (n_out, H) and router.dtype == x.dtype and ids.dtype == torch.int32
@@ -944,7 +1014,8 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     assert logits is None or (logits.dtype == torch.float32 and logits.shape == (T, n_out))
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out)
     _check(lib().fd_moe_route(_ptr(x), _ptr(router), _dt(x.dtype), _ptr(logits), _ptr(correction), _ptr(bias), _ptr(ids),
-                              _ptr(wts), T, H, n_out, top, _stream()))
+                              _ptr(wts), T, H, n_out, top, int(sigmoid_scores), int(n_groups), int(keep_groups),
+                              int(weight_scale is None), float(weight_scale or 0.0), _stream()))
 
 
 def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_pair: torch.Tensor,
@@ -961,20 +1032,23 @@ def moe_align(ids: torch.Tensor, n_experts: int, pair_pos: torch.Tensor, sorted_
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_pair: torch.Tensor,
              tile_expert: torch.Tensor, n_tiles: torch.Tensor, top: int, mt: int, plain: bool = False,
-             gated_limit: Optional[float] = None) -> None:
+             gated_limit: Optional[float] = None, gated_act: Optional[int] = None) -> None:
     """Grouped product with the experts' stacked matrices w [E, N, K].  ``down`` False: a = x [T, K] (rows gathered
     through the grouping), out [cap, N] = relu(x w_e^T)^2 in a's dtype; True: a = the grouped activations [cap, K],
     out [cap, N] in a's dtype.  ``plain`` (with ``down`` False): no activation, out = x w_e^T (a gated activation follows
     in a kernel of its own).  ``mt``: the tile rows the grouping was made with.  bfloat16 with K a multiple of 8 runs on
-    the tensor cores, everything else on the CUDA cores (tiles of 32 rows only)."""
+    the tensor cores, everything else on the CUDA cores (tiles of 32 rows only).  ``gated_limit`` (clamped swish with
+    that limit) or ``gated_act`` (GLU_SILU, GLU_GELU_TANH): w's rows are tiles of 8 gate + 8 up rows and out [cap, N / 2]
+    is the gated activation of each pair."""
     E, N, Kd = w.shape
     cap = sorted_pair.numel()
-    gated = gated_limit is not None       # w rows in tiles of 8 gate + 8 up: out [cap, N / 2] = clamped swish(gate) (up + 1)
+    gated = gated_limit is not None or gated_act is not None
+    act = GLU_CLAMPED if gated_limit is not None else (gated_act or 0)
     assert a.dtype == w.dtype and a.shape[1] == Kd and out.shape == (cap, N // 2 if gated else N)
     assert out.dtype == a.dtype and (not down or a.shape[0] == cap) and not (gated and (down or plain))
     mode = 1 if down else (3 if gated else (2 if plain else 0))
     _check(lib().fd_moe_gemm(_ptr(a), _ptr(w), _ptr(out), _dt(a.dtype), mode, _ptr(sorted_pair), _ptr(tile_expert),
-                             _ptr(n_tiles), cap, mt, top, N, Kd, float(gated_limit or 0.0), _stream()))
+                             _ptr(n_tiles), cap, mt, top, N, Kd, float(gated_limit or 0.0), int(act), _stream()))
 
 
 def moe_gather(x: torch.Tensor, xs: torch.Tensor, sorted_pair: torch.Tensor, n_tiles: torch.Tensor, top: int,
@@ -993,17 +1067,21 @@ def gemm_tc_grouped_supported(N: int, K: int) -> bool:
 
 def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, relu2: bool, tile_expert: torch.Tensor,
                     n_tiles: torch.Tensor, status: Optional[torch.Tensor] = None,
-                    gated_limit: Optional[float] = None) -> None:
+                    gated_limit: Optional[float] = None, gated_act: Optional[int] = None) -> None:
     """Grouped product on the tcgen05 tensor cores: x [cap, K] in row tiles of 128 of which the first ``n_tiles``
     exist, tile t times matrix ``tile_expert[t]`` of the stack w [E, N, K] (both device tensors).  ``relu2``: out
     bfloat16 [cap, N] = max(x w_e^T, 0)^2; else out bfloat16 or float32 [cap, N]."""
     cap, Kd = x.shape
     E, N, _ = w.shape
-    gated = gated_limit is not None   # w rows in tiles of 8 gate + 8 up: out bfloat16 [cap, N / 2] = clamped swish(gate) (up + 1)
+    # w rows in tiles of 8 gate + 8 up: out bfloat16 [cap, N / 2] = clamped swish(gate) (up + 1) with ``gated_limit``, or
+    # ``gated_act`` (GLU_SILU, GLU_GELU_TANH) of gate, times up
+    gated = gated_limit is not None or gated_act is not None
     assert x.dtype == w.dtype == torch.bfloat16 and w.shape[2] == Kd and cap % 128 == 0
     assert out.shape == (cap, N // 2 if gated else N) and not (gated and relu2)
     assert out.dtype in ((torch.bfloat16,) if relu2 or gated else (torch.bfloat16, torch.float32)) and tile_expert.numel() * 128 >= cap
-    mode = 7 if gated else (5 if relu2 else (1 if out.dtype == torch.bfloat16 else 2))
+    mode = 5 if relu2 else (1 if out.dtype == torch.bfloat16 else 2)
+    if gated:
+        mode = 7 if gated_limit is not None else (8 if gated_act == GLU_SILU else 9)
     _check(lib().fd_gemm_tc_grouped(_ptr(x), _ptr(w), _ptr(out), mode, cap, N, Kd, E, _ptr(tile_expert),
                                     _ptr(n_tiles), float(gated_limit or 0.0), _ptr(status), _stream()))
 

@@ -2,7 +2,7 @@
 the parts of the architectures this library ships."""
 
 from . import (attention, block, conv_attention, embedding, head, lanes, mlp, moe, norm, normed_attention,  # noqa: F401
-               parallel, recurrent, rope, stream)  # noqa: F401  (registration)
+               parallel, recurrent, rope, side, stream)  # noqa: F401  (registration)
 from .base import (Block, Embedding, FeedForward, Head, KVRequest, LayerCache, Mixer, Norm, Part, Position,
                    Runtime)
 

@@ -20,16 +20,26 @@ class PreNormBlock(Block):
     davidjoyme/flashdecode-cuda).  Returns the feed-forward's output, still to
     be added by whoever norms next.  A layer without a feed-forward
     (``feed_forward`` None) is x += mixer(norm1(x)) alone; a ``norm2`` it is
-    given all the same declares its tensor and never runs.
+    given all the same declares its tensor and never runs.  ``side``: a
+    ``side_input`` part that runs last; it completes the stream with the
+    pending output and returns its own, x += side(x, tokens).  Norms that add
+    their delta times a constant (``delta_scale``) make every one of these sums
+    x += c * (...).
     """
 
-    def __init__(self, norm1, mixer, norm2=None, feed_forward=None):
-        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+    def __init__(self, norm1, mixer, norm2=None, feed_forward=None, side=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward, self.side = norm1, mixer, norm2, feed_forward, side
         if feed_forward is not None and norm2 is None:
             raise ValueError("a pre-norm layer with a feed-forward needs its second norm")
 
     def parts(self):
-        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward, self.side) if p is not None]
+
+    def stream_state(self, resid: torch.Tensor, delta) -> torch.Tensor:
+        scale = float(getattr(self.norm1, "delta_scale", 1.0))
+        if delta is None or scale == 1.0:
+            return super().stream_state(resid, delta)
+        return resid + scale * (delta.float().sum(0) if delta.dim() == 3 else delta.float())
 
     def first_weights(self) -> Optional[torch.Tensor]:
         return self.mixer.first_weights()
@@ -44,11 +54,14 @@ class PreNormBlock(Block):
         after_block = ctx.upcoming                       # what the step streams after this block (set by the model)
         self.norm1.forward(ctx, delta, resid, xn)
         if self.feed_forward is None:
-            return self.mixer.forward(ctx, xn, lc)
+            d = self.mixer.forward(ctx, xn, lc)
+            return d if self.side is None else self.side.forward(ctx, resid, d)
         ctx.upcoming = self.feed_forward.first_weights()
         d1 = self.mixer.forward(ctx, xn, lc)
         self.norm2.forward(ctx, d1, resid, xn)
         ctx.upcoming = after_block
+        if self.side is not None:
+            return self.side.forward(ctx, resid, self.feed_forward.forward(ctx, xn))
         # float partial sums only if whoever adds this block's output has said it takes them
         if ctx.delta_parts_ok and getattr(self.feed_forward, "offers_parts", False):
             return self.feed_forward.forward(ctx, xn, parts_ok=True)

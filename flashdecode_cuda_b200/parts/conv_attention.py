@@ -40,7 +40,11 @@ class ConvGatedAttention(Mixer):
     positions below it stay visible, at their true positions); ``sink`` (``.sink`` [heads]: exp(sink_h) is one more
     term of head h's softmax denominator, with no key and no value); ``talk`` (``.talk`` [heads, heads]: after the
     softmax the heads' weights are mixed, a'_h = sum_g talk[h, g] a_g, and head h applies a'_h to the values of its
-    own key/value head).  Scores, softmax, the sink and the mixing are float32 in both dtypes.
+    own key/value head).  ``sink="unit"``: the keyless term is the constant 1 (a score of zero) and has no tensor.
+    ``qk_norm`` (an eps): every head of q and of k is RMS-normed over its dimensions with the weights ``.q.norm`` /
+    ``.k.norm`` [head_dim], shared by the heads, after the convolution and before the rotation.  ``values_from_keys``:
+    there is no value projection; a key head's values are its convolved keys as they stand before norm and rotation.
+    Scores, softmax, the sink, the norms and the mixing are float32 in both dtypes.
 
     The last ``taps - 1`` projected values (before the convolution) of every sequence are its state, kept in
     float32 per cache slot; keys (rotated) and values (both after the convolution) go to the paged cache.
@@ -51,7 +55,8 @@ class ConvGatedAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
                  taps: int, scale: float, position=None, rot_dims: int = 0, chunk: Optional[int] = None,
                  window: Optional[int] = None, gate: bool = True, bias: bool = False, interleaved: bool = False,
-                 softcap: Optional[float] = None, keep_first: int = 0, sink: bool = False, talk: bool = False):
+                 softcap: Optional[float] = None, keep_first: int = 0, sink=False, talk: bool = False,
+                 qk_norm: Optional[float] = None, values_from_keys: bool = False):
         for what, n in (("head size", head_dim), ("value head size", v_head_dim)):
             if n < 1 or _up8(n) > 256:
                 raise ValueError(f"{prefix}: {what} {n} is not taken: the attention kernels take sizes from 1 to 256")
@@ -73,16 +78,26 @@ class ConvGatedAttention(Mixer):
             raise ValueError(f"{prefix}: the scores' soft cap must be positive, got {softcap}")
         if keep_first < 0 or (talk and gate):
             raise ValueError(f"{prefix}: keep_first must not be negative, and mixed heads take no gate")
+        if sink not in (False, True, "unit"):
+            raise ValueError(f"{prefix}: sink must be False, True (a learned term per head) or 'unit', got {sink!r}")
+        if values_from_keys and v_head_dim != head_dim:
+            raise ValueError(f"{prefix}: values taken from the keys have the keys' size {head_dim}, not {v_head_dim}")
+        if qk_norm is not None and not qk_norm > 0:
+            raise ValueError(f"{prefix}: the eps of the q and k norm must be positive, got {qk_norm}")
         self.bias, self.interleaved, self.softcap = bool(bias), bool(interleaved), softcap
         self.keep_first, self.sink, self.talk = int(keep_first) if window else 0, bool(sink), bool(talk)
+        self.unit_sink = sink == "unit"
+        self.qk_norm, self.values_from_keys = qk_norm, bool(values_from_keys)
         # the options only the CUDA-core attention kernel has
         self.extended = bool(softcap or self.keep_first or sink or talk)
-        self.n_conv = (n_heads + n_kv_heads) * self.d + n_kv_heads * self.dv     # channels that are convolved
+        # channels that are convolved
+        self.n_conv = (n_heads + n_kv_heads) * self.d + (0 if values_from_keys else n_kv_heads * self.dv)
 
     # --- what it needs -------------------------------------------------
     def _sizes(self):
-        """(tensor, channels as stored) of the three convolved projections."""
-        return (("q", self.n_q * self.d_true), ("k", self.n_kv * self.d_true), ("v", self.n_kv * self.dv_true))
+        """(tensor, channels as stored) of the convolved projections."""
+        qk = (("q", self.n_q * self.d_true), ("k", self.n_kv * self.d_true))
+        return qk if self.values_from_keys else qk + (("v", self.n_kv * self.dv_true),)
 
     def _padded(self, name: str, t: torch.Tensor) -> torch.Tensor:
         """A tensor whose rows are the channels of q, k or v, with zero rows up to the padded head size."""
@@ -98,7 +113,10 @@ class ConvGatedAttention(Mixer):
             specs.append(TensorSpec(f"{p}.{n}.conv", (c, self.taps), "vector", init="conv"))
             if self.bias:
                 specs.append(TensorSpec(f"{p}.{n}.b", (c,), "vector", init="bias"))
-        if self.sink:
+        if self.qk_norm is not None:
+            specs += [TensorSpec(f"{p}.q.norm", (self.d_true,), "vector", init="norm"),
+                      TensorSpec(f"{p}.k.norm", (self.d_true,), "vector", init="norm")]
+        if self.sink and not self.unit_sink:
             specs.append(TensorSpec(f"{p}.sink", (self.n_q,), "vector", init="sink"))
         if self.talk:
             specs.append(TensorSpec(f"{p}.talk", (self.n_q, self.n_q), "vector", init="lane_mix"))
@@ -130,7 +148,15 @@ class ConvGatedAttention(Mixer):
             self.b_in = torch.cat(b).contiguous()
         self.conv_w = torch.cat([self._padded(n, tensors.pop(f"{p}.{n}.conv").float()) for n, _ in self._sizes()],
                                 dim=0).contiguous()
-        self.sink_w = tensors.pop(f"{p}.sink").float().contiguous() if self.sink else None
+        self.sink_w = None
+        if self.unit_sink:
+            self.sink_w = torch.zeros(self.n_q, dtype=torch.float32, device=rt.device)
+        elif self.sink:
+            self.sink_w = tensors.pop(f"{p}.sink").float().contiguous()
+        self.q_norm_w = self.k_norm_w = None
+        if self.qk_norm is not None:         # zero weights on the padded dimensions; the mean runs over the true ones
+            self.q_norm_w = _pad_heads(tensors.pop(f"{p}.q.norm").float(), 1, self.d_true, self.d).contiguous()
+            self.k_norm_w = _pad_heads(tensors.pop(f"{p}.k.norm").float(), 1, self.d_true, self.d).contiguous()
         self.talk_w = tensors.pop(f"{p}.talk").float().contiguous() if self.talk else None
         self.w_o = tensors[f"{p}.o"]
         if self.dv != self.dv_true:         # zero columns where the padded value dimensions arrive
@@ -171,7 +197,8 @@ class ConvGatedAttention(Mixer):
                            rope.sin if self.rot_dims else None, self.rot_dims, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                            ctx.row_q_start, ctx.row_q_len, lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv,
                            self.d, self.dv, lc.writes, single and lc.writes, rt.status, interleaved=self.interleaved,
-                           first_col=col0)
+                           first_col=col0, q_norm=self.q_norm_w, k_norm=self.k_norm_w, norm_eps=self.qk_norm or 0.0,
+                           norm_count=self.d_true, values_from_keys=self.values_from_keys)
         if state is not None and lc.writes and not single:
             K.conv_state_update(proj, state, ctx.row_slot, ctx.row_q_start, ctx.row_q_len, ctx.n_rows, first_col=col0)
         heads_out = self.n_q * (self.n_kv if self.talk else 1)      # mixed heads: every head's weights on every value head

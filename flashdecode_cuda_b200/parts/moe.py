@@ -39,7 +39,11 @@ class RoutedExperts(FeedForward):
     down(g sigmoid(1.702 g) (u + 1)) (tensors ``.e<i>.gate`` too).  ``router_bias``: ``<prefix>.router.b`` is added to
     the router's outputs before the softmax; w is then the softmax over the chosen outputs alone.  The last
     ``n_identity`` router outputs are identity experts: they have no tensors and pass h on.  ``shared_ff``
-    None: no shared expert.
+    None: no shared expert.  ``expert_act = "silu_gated"``: an expert is down(silu(gate h) * (up h)).
+    ``score = "sigmoid"``: s = sigmoid(W_router h), each output by itself.  ``groups = (count, keep)``: the router's
+    outputs form ``count`` equal groups of neighbours; a group ranks by the sum of its two largest s + correction, and
+    only outputs of the best ``keep`` groups can be chosen.  ``weight_scale``: w = s[chosen] * weight_scale, not
+    divided by the chosen scores' sum.
 
     All decisions are taken on the device (no read-back): the (token, choice) pairs are grouped by expert, each
     group padded to whole row tiles, and two grouped products run over the tiles that exist.  Tensors:
@@ -49,15 +53,30 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, prefix: str, hidden_size: int, n_experts: int, top: int, expert_ff: int, n_identity: int = 0,
                  shared_ff: Optional[int] = None, correction: bool = True, expert_act: str = "relu2",
-                 limit: Optional[float] = None, router_bias: bool = False):
+                 limit: Optional[float] = None, router_bias: bool = False, score: str = "softmax",
+                 groups: Optional[tuple] = None, weight_scale: Optional[float] = None):
         if n_experts < 0 or n_identity < 0 or not (1 <= top <= n_experts + n_identity) or expert_ff < 1:
             raise ValueError(f"{prefix}: {top} choices among {n_experts} experts and {n_identity} identity experts")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.E, self.n_identity, self.top, self.ff, self.shared_ff = n_experts, n_identity, top, expert_ff, shared_ff
         self.has_correction = correction
-        if expert_act not in ("relu2", "clamped_swish") or (expert_act == "clamped_swish" and not (limit and limit > 0)):
-            raise ValueError(f"{prefix}: expert activation {expert_act!r} (relu2, or clamped_swish with a positive limit)")
-        self.gated, self.limit, self.router_bias = expert_act == "clamped_swish", limit, bool(router_bias)
+        if expert_act not in ("relu2", "clamped_swish", "silu_gated") or (expert_act == "clamped_swish" and not (limit and limit > 0)):
+            raise ValueError(f"{prefix}: expert activation {expert_act!r} (relu2, silu_gated, or clamped_swish with a positive limit)")
+        self.gated, self.router_bias = expert_act in ("clamped_swish", "silu_gated"), bool(router_bias)
+        self.limit = limit if expert_act == "clamped_swish" else None
+        self.glu_kind = K.GLU_CLAMPED if expert_act == "clamped_swish" else K.GLU_SILU
+        # how the grouped products' gated epilogues are told the activation
+        self.gated_args = dict(gated_limit=limit) if expert_act == "clamped_swish" else dict(gated_act=K.GLU_SILU)
+        if score not in ("softmax", "sigmoid"):
+            raise ValueError(f"{prefix}: router scores {score!r} (softmax or sigmoid)")
+        self.sigmoid_scores = score == "sigmoid"
+        n_out = n_experts + n_identity
+        self.n_groups, self.keep_groups = (1, 1) if not groups else (int(groups[0]), int(groups[1]))
+        if (self.n_groups < 1 or n_out % self.n_groups or not (1 <= self.keep_groups <= self.n_groups)
+                or self.keep_groups * (n_out // self.n_groups) < top):
+            raise ValueError(f"{prefix}: {self.keep_groups} of {self.n_groups} groups of {n_out} router outputs for "
+                             f"{top} choices: the groups must be equal and the kept ones hold enough outputs")
+        self.weight_scale = None if weight_scale is None else float(weight_scale)
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H = self.prefix, self.hidden_size
@@ -142,7 +161,9 @@ class RoutedExperts(FeedForward):
             # token's scores do not change by a bit with its neighbours
             logits = ws.get("moe_logits", (T, self.router.shape[0]), torch.float32)
             matmul(x, self.router, None, logits, status=self.rt.status)
-        K.moe_route(x, self.router, self.correction, ids, wts, logits, bias=self.r_bias)
+        K.moe_route(x, self.router, self.correction, ids, wts, logits, bias=self.r_bias,
+                    sigmoid_scores=self.sigmoid_scores, n_groups=self.n_groups, keep_groups=self.keep_groups,
+                    weight_scale=self.weight_scale)
         # (the routed experts follow on the main stream; the shared expert's stream joins before the combine)
         y = pair_pos = None
         pair_pos = ws.get("moe_pair_pos", (T * top,), torch.int32)
@@ -164,20 +185,20 @@ class RoutedExperts(FeedForward):
                 xs = ws.get("moe_xs", (cap, H), x.dtype)
                 K.moe_gather(x, xs, sorted_pair, n_tiles, top, mt)
                 if fused and n_up % 32 == 0:
-                    K.gemm_tc_grouped(xs, self.w_up, act, False, tile_expert, n_tiles, self.rt.status, gated_limit=self.limit)
+                    K.gemm_tc_grouped(xs, self.w_up, act, False, tile_expert, n_tiles, self.rt.status, **self.gated_args)
                 elif self.gated:
                     gu = ws.get("moe_gu", (cap, n_up), x.dtype)
                     K.gemm_tc_grouped(xs, self.w_up, gu, False, tile_expert, n_tiles, self.rt.status)
-                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit, tiled=self.tiled)
+                    K.glu_mul(gu, act, self.glu_kind, self.limit or 0.0, tiled=self.tiled)
                 else:
                     K.gemm_tc_grouped(xs, self.w_up, act, True, tile_expert, n_tiles, self.rt.status)
                 K.gemm_tc_grouped(act, self.w_down, y, False, tile_expert, n_tiles, self.rt.status)
             else:
                 if fused:
-                    K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt, gated_limit=self.limit)
+                    K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt, **self.gated_args)
                 elif self.gated:
                     K.moe_gemm(x, self.w_up, gu, False, sorted_pair, tile_expert, n_tiles, top, mt, plain=True)
-                    K.glu_mul(gu, act, K.GLU_CLAMPED, self.limit)
+                    K.glu_mul(gu, act, self.glu_kind, self.limit or 0.0)
                 else:
                     K.moe_gemm(x, self.w_up, act, False, sorted_pair, tile_expert, n_tiles, top, mt)
                 K.moe_gemm(act, self.w_down, y, True, sorted_pair, tile_expert, n_tiles, top, mt)

@@ -25,12 +25,15 @@ class RMSNorm(Norm):
     accepts_parts = True        # the kernel adds up to four float partial sums in order while it adds the residual
 
     def __init__(self, prefix: str, size: int, eps: float, unit_offset: bool = False, tensor: Optional[str] = None,
-                 optional: bool = False):
+                 optional: bool = False, delta_scale: Optional[float] = None):
         """``unit_offset``: the checkpoint holds the gain's offset from one and the norm multiplies by 1 + weight (added in
         float32 when the weights are bound).  ``tensor``: the weight's full name where it is not
-        ``<prefix>.weight``.  ``optional``: a checkpoint may lack the weight (a norm that never runs)."""
+        ``<prefix>.weight``.  ``optional``: a checkpoint may lack the weight (a norm that never runs).
+        ``delta_scale``: a model whose sub-layers enter the stream times a constant, x += c f(norm(x)): the pending
+        output is multiplied by c (in float32) as this norm adds it."""
         self.name = tensor or f"{prefix}.weight"
         self.size, self.eps, self.unit_offset, self.optional = size, float(eps), bool(unit_offset), bool(optional)
+        self.delta_scale = 1.0 if delta_scale is None else float(delta_scale)
 
     def tensor_specs(self) -> List[TensorSpec]:
         return [TensorSpec(self.name, (self.size,), "vector", optional=self.optional,
@@ -46,7 +49,7 @@ class RMSNorm(Norm):
                 rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,
                 write_resid: bool = True, n_parts: int = 1) -> None:
         K.add_rmsnorm(delta, resid, self.weight, self.eps, out, rows=rows, n_out=n_out,
-                      write_resid=write_resid, n_parts=n_parts)
+                      write_resid=write_resid, n_parts=n_parts, delta_scale=self.delta_scale)
 
 
 @register_part("norm", "dyn_tanh")

@@ -157,3 +157,74 @@ class GatedLinearRecurrence(_StateMixer):
                       lc.writes, self.rt.status, lower=self.lower, max_q_len=ctx.max_q_len, scratch=self.scan_scratch(ctx))
         K.head_norm_gate(o, act, act_col, self.n_heads, self.dv, self.eps, self.norm_w, None, 0, scale)
         return act
+
+
+@register_part("mixer", "channel_decay_attention")
+class ChannelDecayAttention(_StateMixer):
+    """Linear attention with a decay per key channel that follows the input.  For the mixer's input h [T, hidden], per
+    head:
+
+        q = W_q h * head_dim^(-1/2);  k = W_k h;  v = W_v h                           (no biases)
+        a = sigmoid(W_a2 (W_a1 h) + b_a2)^(1 / tau)                                   per channel of k, through a narrow W_a1
+        S_t = diag(a_t) S_(t-1) + k_t v_t^T;   o_t = S_t^T q_t
+        out = W_o ( concat_h o_t / rms(o_t) * w * silu(W_g h) )                       (w [v_head_dim], shared by heads)
+
+    The state starts at zero and is carried in float32 per cache slot; the decay's pre-activation leaves its product as
+    float32, and the sigmoid, its logarithm, the power, the state, the output and the norm are float32 in both dtypes.
+    Tensors ``<prefix>.q`` / ``.k`` / ``.v`` / ``.g`` / ``.o`` / ``.norm`` / ``.a1`` / ``.a2`` / ``.a2.b``.
+    ``decay_rank`` (the rows of W_a1) None: the checkpoint's tensors give it."""
+
+    shares_products = False
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, head_dim: int, v_head_dim: int,
+                 tau: float, eps: float, decay_rank: Optional[int] = None):
+        if head_dim > 256 or min(n_heads, head_dim, v_head_dim, 1 if decay_rank is None else decay_rank) < 1:
+            raise ValueError(f"{prefix}: heads of {head_dim} x {v_head_dim}: the recurrence takes key sizes up to 256")
+        if not tau > 0:
+            raise ValueError(f"{prefix}: the decay's temperature must be positive, got {tau}")
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.n_heads, self.d, self.dv, self.rank = n_heads, head_dim, v_head_dim, decay_rank
+        self.tau, self.eps = float(tau), float(eps)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H = self.prefix, self.hidden_size
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        return [TensorSpec(f"{p}.q", (nk, H), init="unit"), TensorSpec(f"{p}.k", (nk, H), init="unit"),
+                TensorSpec(f"{p}.v", (nv, H), init="unit"), TensorSpec(f"{p}.g", (nv, H), init="unit"),
+                TensorSpec(f"{p}.o", (H, nv), init="unit"), TensorSpec(f"{p}.norm", (self.dv,), "vector", init="norm"),
+                TensorSpec(f"{p}.a1", (self.rank, H), init="unit"), TensorSpec(f"{p}.a2", (nk, self.rank), init="unit"),
+                TensorSpec(f"{p}.a2.b", (nk,), "vector", init="decay_bias")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n in "qkvg"], dim=0).contiguous()
+        self.b_in = None
+        self.w_a1, self.w_a2 = tensors[f"{p}.a1"], tensors[f"{p}.a2"]
+        if self.w_a1.shape[0] != self.w_a2.shape[1]:
+            raise ValueError(f"{p}: a1 has {self.w_a1.shape[0]} rows and a2 {self.w_a2.shape[1]} columns")
+        self.rank = self.w_a1.shape[0]
+        self.b_a2 = tensors.pop(f"{p}.a2.b").float().contiguous()
+        self.norm_w = tensors.pop(f"{p}.norm").float().contiguous()
+        self.w_o = tensors[f"{p}.o"]
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes() + (self.w_a1.numel() + self.w_a2.numel()) * self.w_a1.element_size()
+
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, ws, rt = ctx.T, ctx.ws, self.rt
+        nk, nv = self.n_heads * self.d, self.n_heads * self.dv
+        proj = ws.get("rec_proj", (T, self.w_in.shape[0]), x.dtype)
+        matmul(x, self.w_in, None, proj, status=rt.status)
+        low = ws.get("rec_decay_low", (T, self.rank), x.dtype)
+        matmul(x, self.w_a1, None, low, status=rt.status)
+        z = ws.get("rec_decay_z", (T, nk), torch.float32)
+        matmul(low, self.w_a2, self.b_a2, z, status=rt.status)
+        o = ws.get("scan_out", (T, nv), torch.float32)
+        K.linear_scan(proj, 0, nk, 2 * nk, lc.states["state"], o, K.SCAN_CHANNEL_DECAY, ctx.row_slot, ctx.row_q_start,
+                      ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv, lc.writes, rt.status,
+                      max_q_len=ctx.max_q_len, scratch=self.scan_scratch(ctx), gate=z, q_scale=self.d ** -0.5, tau=self.tau)
+        act = ws.get("rec_act", (T, nv), x.dtype)
+        K.head_norm_gate(o, act, 0, self.n_heads, self.dv, self.eps, self.norm_w, proj, 2 * nk + nv, 1.0)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        return matmul(act, self.w_o, None, out, target_ctas=4 * rt.sm_count, status=rt.status, upcoming=ctx.upcoming)

@@ -69,6 +69,9 @@ class RotaryScaled(Position):
         f_i <- f_i / factor * ramp_i + f_i * (1 - ramp_i);   cos, sin <- (0.1 ln(factor) + 1) * cos, sin
 
     so pairs that turn fast keep their frequency, slow ones are divided by ``factor``, with a linear ramp between.
+    ``scaling`` = {factor, low, high, original} is the other form, by wavelength l_i = 2 pi / f_i: l_i < original / high
+    keeps f_i; l_i > original / low gives f_i / factor; between them, with s = (original / l_i - low) / (high - low),
+    f_i <- (1 - s) f_i / factor + s f_i; cos and sin are not rescaled.
     The tables are computed in float64 on the host and rounded once.  They grow with the first cache (there is no
     longest sequence in the configuration) and are never replaced afterwards, like those of ``rotary_half``."""
 
@@ -89,6 +92,13 @@ class RotaryScaled(Position):
             return f, 1.0
         sc = self.scaling
         factor, orig = float(sc["factor"]), float(sc["original"])
+        if "low" in sc:                                  # by wavelength
+            low, high = float(sc["low"]), float(sc["high"])
+            wavelength = 2.0 * math.pi / f
+            s = ((orig / wavelength - low) / (high - low)).clamp(0.0, 1.0) if high != low else torch.ones_like(f)
+            blended = (1.0 - s) * f / factor + s * f
+            out = torch.where(wavelength < orig / high, f, torch.where(wavelength > orig / low, f / factor, blended))
+            return out, 1.0
 
         def pair(turns: float) -> float:
             return self.dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))

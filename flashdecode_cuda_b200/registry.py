@@ -7,7 +7,8 @@
   chosen through this table.
 * ``PARTS``: (kind, name) -> the class that implements a part.  Kinds are
   ``embedding``, ``position``, ``norm``, ``mixer``, ``feed_forward``, ``block``,
-  ``head`` and ``stream_op``.  A blueprint names parts by (kind, name); nothing else in the
+  ``head``, ``stream_op``, ``table`` (a lookup table several parts share) and
+  ``side_input`` (what a layer adds from the token itself).  A blueprint names parts by (kind, name); nothing else in the
   engine knows a part's class.
 
 A new architecture or part is added by calling ``register_architecture`` /
@@ -20,7 +21,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Dict, Tuple, Type
 
-PART_KINDS = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head", "stream_op")
+PART_KINDS = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head", "stream_op", "table",
+              "side_input")
 
 
 @dataclass(frozen=True)

@@ -41,6 +41,11 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _shape_fits(shape, declared) -> bool:
+    """A declared size of None is one that only the checkpoint gives."""
+    return len(shape) == len(declared) and all(d is None or int(n) == int(d) for n, d in zip(shape, declared))
+
+
 def check(specs: Iterable[TensorSpec], tensors: Dict[str, torch.Tensor]) -> None:
     """Raise ``WeightError`` unless ``tensors`` holds exactly what ``specs``
     declare (optional ones may be absent), each with the declared shape."""
@@ -51,7 +56,7 @@ def check(specs: Iterable[TensorSpec], tensors: Dict[str, torch.Tensor]) -> None
     wrong = []
     for s in specs:
         t = tensors.get(s.name)
-        if t is not None and tuple(t.shape) != tuple(s.shape):
+        if t is not None and not _shape_fits(t.shape, s.shape):
             wrong.append(f"{s.name}: expected {tuple(s.shape)}, got {tuple(t.shape)}")
         if t is not None and s.kind != "table" and not t.dtype.is_floating_point:
             wrong.append(f"{s.name}: expected a floating-point tensor, got {t.dtype}")
@@ -93,6 +98,9 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
     are made does not matter.  Values are drawn in float32 and rounded."""
     if spec.kind == "table":
         raise ValueError(f"{spec.name}: integer tables have no random initialiser")
+    if any(d is None for d in spec.shape):
+        raise ValueError(f"{spec.name}: shape {tuple(spec.shape)} has a size that only a checkpoint gives; "
+                         f"name it in the configuration to draw random weights")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.init == "zeros":
@@ -117,6 +125,10 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
             t = 0.5 * t
         elif spec.init == "unit_interval":      # lower bounds of a gate: inside (0, 1)
             t = torch.sigmoid(t)
+        elif spec.init == "decay_bias":         # pre-activation of a decay near one: sigmoid(2 + N(0, 1))
+            t = 2.0 + t
+        elif spec.init == "unit_rows":          # rows of a lookup table whose entries multiply activations: about one
+            pass
         elif spec.init in ("normal", "bias", "embedding"):
             t = 0.02 * t
         else:
