@@ -156,7 +156,7 @@ def gla_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, mc: dict, eps
 def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, mc: dict, eps: float,
                     capture: Optional[dict] = None) -> torch.Tensor:
     S = h.shape[0]
-    H, G, d = mc["heads"], mc["kv_heads"], mc["dim"]
+    H, G, d = mc["heads"], mc.get("kv_heads", mc["heads"]), mc["dim"]
     q = h @ W[f"{p}.q"].T + W[f"{p}.q.b"]
     k = h @ W[f"{p}.k"].T + W[f"{p}.k.b"]
     q = short_conv(q, W[f"{p}.q.conv"]).view(S, H, d)
@@ -195,7 +195,7 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, rc: d
         choice = torch.where(allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), choice,
                              torch.full_like(choice, -math.inf))
     ids = choice.topk(top, dim=-1).indices
-    return ids, s.gather(1, ids) * float(rc["scale"])
+    return ids, s.gather(1, ids) * float(rc.get("scale", 1.0))
 
 
 def moe_ff(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, fc: dict, capture: Optional[dict] = None):
@@ -237,8 +237,8 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.flo
     """Logits [S, vocab] of one whole sequence (and, on request, the stream after every layer run)."""
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    eps, m = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
-    x = W["embed"][tokens] * float(cfg["embedding"]["scale"])
+    eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
+    x = W["embed"][tokens] * float(cfg.get("embedding", {}).get("scale", 1.0))
     side = cfg.get("token_side")
     layers = []
     for i, t in layer_runs(cfg):
