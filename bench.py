@@ -29,7 +29,9 @@ benchmark configuration says; the library's own default of 64 is measured
 beside it (``points.decode_b8_block64``, ``points.prefill_block64_ms``).
 
 ``--compare nizazen`` does the same for the Nizazen design (eight layers that alternate windowed and latent attention,
-dense and routed feed-forwards, on a residual stream of several lanes).  ``--compare revelix`` for the Revelix design (eight layers that alternate retention and attention beside a gated
+dense and routed feed-forwards, on a residual stream of several lanes).  ``--compare botusun`` measures the Botusun design (six
+layers, two of them twice: linear attention with a decay per key channel and windowed attention over convolved, normed keys, dense and routed
+feed-forwards, a contribution of the token itself after every layer) beside the Revelix design at equal sizes.  ``--compare revelix`` for the Revelix design (eight layers that alternate retention and attention beside a gated
 recurrence, each with a dense feed-forward).  ``--compare lonasun`` leaves all of that aside and measures the Lonasun design beside the Qwen2 dense decoder of the
 same width, heads, layer runs and feed-forward work per token (random weights, a window as long as Lonasun's chunk):
 prefill and decode throughput of both at a few layer sizes, and for every mixer and feed-forward the device time of
@@ -388,8 +390,33 @@ def revelix_configs(sz: dict):
     return reve, qwen
 
 
-COMPARISONS = {"lonasun": (COMPARE_SIZES, compare_configs), "nizazen": (NIZAZEN_SIZES, nizazen_configs),
-               "revelix": (REVELIX_SIZES, revelix_configs)}
+def botusun_configs(sz: dict):
+    """(Botusun config dictionary, Revelix config dictionary) of equal width and layer runs.  Botusun: six layers of which
+    two run twice (eight runs), alternating linear attention with a decay per key channel and windowed attention over
+    convolved, normed keys that are their own values, feed-forwards dense and routed in turn, and the token's own
+    contribution after every layer.  Beside it the closest design the library has, Revelix at the sizes of
+    ``--compare revelix``: the same attention heads, head size, window, taps and rotated dimensions, recurrences with the
+    retention layers' heads, and feed-forwards of the same operations per token (three matrices here, two there)."""
+    reve, _ = revelix_configs(sz)
+    inter = int(round(sz["ff"] * 2 / 3 / 64)) * 64
+    att = {"conv": sz["taps"], "dim": sz["dim"], "heads": sz["heads"], "kv_heads": sz["kv"], "mask": {"size": sz["window"]},
+           "rot": {"base": 1000000.0, "dims": sz["rot"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}},
+           "scale": sz["dim"] ** -0.5, "vdim": sz["dim"]}
+    lin = {"dim": sz["ret_dim"], "heads": sz["ret_heads"], "vdim": sz["ret_vdim"], "tau": 16.0, "rank": 64}
+    dense = {"ff": inter, "kind": "dense"}
+    moe = {"expert": {"ff": inter // 4}, "kind": "moe",
+           "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}, "scale": 2.5}}
+    kinds = [("gla", lin, dense), ("attention", att, moe), ("gla", lin, moe), ("attention", att, dense),
+             ("gla", lin, dense), ("attention", att, moe)]
+    botu = {"architecture": "Botusun", "vocab": COMPARE_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 8.0}, "residual_mult": 0.5, "token_side": {"dim": 64},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in kinds], "loop": {"start": 2, "stop": 4, "times": 2}}
+    return botu, reve
+
+
+# design -> (sizes, function of a size that gives both configurations, the key of the model that stands beside it)
+COMPARISONS = {"lonasun": (COMPARE_SIZES, compare_configs, "qwen2"), "nizazen": (NIZAZEN_SIZES, nizazen_configs, "qwen2"),
+               "revelix": (REVELIX_SIZES, revelix_configs, "qwen2"), "botusun": (REVELIX_SIZES, botusun_configs, "revelix")}
 
 
 def compare_one(cfgd: dict, pk: dict, batch: int, context: int, prompt: int, steps: int, warmup: int, seed: int) -> dict:
@@ -500,22 +527,24 @@ def compare_main(args) -> int:
     clocks.start()
     sizes = {}
     design = args.compare
-    table, configs = COMPARISONS[design]
+    table, configs, beside = COMPARISONS[design]
     for name in (args.compare_sizes.split(",") if args.compare_sizes else table):
         ours, qwen = configs(table[name])
-        entry = {"sizes": table[name], "dense_intermediate": qwen["intermediate_size"]}
-        for key, cfgd in ((design, ours), ("qwen2", qwen)):
+        entry = {"sizes": table[name]}
+        if "intermediate_size" in qwen:
+            entry["dense_intermediate"] = qwen["intermediate_size"]
+        for key, cfgd in ((design, ours), (beside, qwen)):
             entry[key] = compare_one(cfgd, pk, args.batch, 2048, 2048, min(args.steps, 64), max(3, args.warmup), args.seed)
             torch.cuda.empty_cache()
         entry["ratios"] = {
-            "prefill_tok_s": round(entry[design]["prefill"]["tok_s"] / entry["qwen2"]["prefill"]["tok_s"], 3),
-            "decode_tok_s": round(entry[design]["decode"]["tok_s"] / entry["qwen2"]["decode"]["tok_s"], 3)}
+            "prefill_tok_s": round(entry[design]["prefill"]["tok_s"] / entry[beside]["prefill"]["tok_s"], 3),
+            "decode_tok_s": round(entry[design]["decode"]["tok_s"] / entry[beside]["decode"]["tok_s"], 3)}
         for phase in ("prefill", "decode"):
             for part in ("mixer", "feed_forward"):
-                a, b = entry[design][phase]["parts"][part], entry["qwen2"][phase]["parts"][part]
+                a, b = entry[design][phase]["parts"][part], entry[beside][phase]["parts"][part]
                 entry["ratios"][f"{phase}_{part}_frac"] = [a["frac"], b["frac"], round(a["frac"] / b["frac"], 3)]
         sizes[name] = entry
-    print(json.dumps({"compare": design, "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic: random weights",
+    print(json.dumps({"compare": design, "beside": {"qwen2": "Qwen2ForCausalLM", "revelix": "Revelix"}[beside], "dtype": "bf16", "data": "synthetic: random weights",
                       "peaks": pk, "batch": args.batch, "prompt": 2048, "context": 2048, "block_size": LIB_BLOCK_SIZE,
                       "clocks": clocks.stop(), "sizes": sizes}))
     return 0
@@ -731,7 +760,7 @@ def main() -> int:
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32: the main run through the true 32-bit path (with --no-points)")
-    ap.add_argument("--compare", default="", choices=["", "lonasun", "nizazen", "revelix"],
+    ap.add_argument("--compare", default="", choices=["", "lonasun", "nizazen", "revelix", "botusun"],
                     help="measure this design beside the closest dense model at equal sizes instead of the default run")
     ap.add_argument("--compare-sizes", default="", help="with --compare: names of the sizes to run, with commas (default: all)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],

@@ -424,6 +424,8 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
             p.part_acc[pi * D + j] = a;
             if (j == 0) { p.part_m[pi] = m * scale_log2 * LN2; p.part_l[pi] = l; }   // natural-log units for the merge
         } else {
+            // a keyless term exp(sink[h]) joins the denominator (the maxima are raw scores: both in units of log2)
+            if (p.sink != nullptr && l > 0.f) l += exp2f(p.sink[kvh * G + r] * 1.4426950408889634f - m * scale_log2);
             static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
         }
     }
@@ -483,6 +485,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
             lsum += ls * w;
         }
         lsum = warp_sum(lsum);
+        if (p.sink != nullptr && lsum > 0.f) lsum += expf(p.sink[kvh * G + r] - m);       // the keyless term, once per head
         const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
         for (int s = lane; s < ns; s += 32) wgt[r * ns + s] *= inv;
     }

@@ -480,6 +480,9 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                v_rep, n_kv);
     const bool ext = softcap > 0.f || (keep_first > 0 && window > 0) || sink != nullptr || v_rep > 1 || out_f32;
     if (ext) use_mma = 0;
+    // of the options the tensor-core decode kernel has the keyless term: a decode step that asks for nothing else runs there
+    const bool sink_only = sink != nullptr && !(softcap > 0.f) && !(keep_first > 0 && window > 0) && v_rep == 1 && !out_f32;
+    const bool decode_mma = (use_mma != 0 || (sink_only && ext_mma != 0)) && dtype == 1 && max_q_len == 1 && dv == d;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
     FD_REQUIRE(d % 8 == 0 && d >= 8 && d <= D_MAX, -2, "attention: head size %d must be a multiple of 8 in [8, %d]", d, D_MAX);
@@ -520,7 +523,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.QT = qt; p.n_splits = n_splits; p.split_len = split_len; p.window = window; p.scale = scale;
 
     int rc = 1;
-    if (use_mma && dtype == 1 && max_q_len == 1) {
+    if (decode_mma) {
         AttnParams pd = p;
         const int cut = fd_attn_decode_group(G, d, dv);     // a large group as several smaller ones on the same pool head
         if (cut > 0 && cut < G) { pd.G = cut; pd.kv_div = G / cut; pd.n_kv = n_kv * (G / cut); }
@@ -639,17 +642,20 @@ extern "C" int fd_attention_mma_sync(const void* q, const void* k_pool, const vo
 // use_mma is set): softcap > 0 caps the scaled scores by a tanh; keep_first: with a window, the
 // first so many positions stay visible; sink [n_q] (or null): a keyless term exp(sink[h]) in head h's denominator;
 // v_rep == n_kv: every query head's weights are applied to all value heads and out is [T, n_q, n_kv, dv] (scratch for
-// the split form: fd_attn_scratch_floats(T, n_q * n_kv, dv, n_splits)); out_f32: out is float.
+// the split form: fd_attn_scratch_floats(T, n_q * n_kv, dv, n_splits)); out_f32: out is float.  Decode steps in bfloat16
+// whose only option is the keyless term run on the tensor-core decode kernel when use_mma is set and it takes the sizes
+// (counters: as for fd_attention, the kernel then merges its own splits).
 extern "C" int fd_attention_ext(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                                 const int* block_table, int max_blocks, int num_blocks, int block_size,
                                 const int* tok_row, const int* row_slot, const int* row_q_start,
                                 const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window, int dv, int chunk,
                                 int n_splits, int split_len, float* scratch, int* status, float softcap, int keep_first,
-                                const float* sink, int v_rep, int out_f32, int use_mma, cudaStream_t stream) {
+                                const float* sink, int v_rep, int out_f32, int use_mma, int* counters,
+                                cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, dv, chunk, n_splits, split_len, scratch, nullptr, status, 0, stream, nullptr, 0,
+                          window, dv, chunk, n_splits, split_len, scratch, counters, status, 0, stream, nullptr, 0,
                           softcap, keep_first, sink, v_rep, out_f32, use_mma);
 }
 

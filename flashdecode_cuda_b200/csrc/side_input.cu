@@ -8,9 +8,10 @@
 //
 //  * add_cast: x as above, written back to resid and, rounded once, to a matrix for the product with G;
 //  * side_gate_mul: g from z = G x (float) and the table row of every token;
-//  * token_side_row: all of it in one launch for steps of few tokens, a CTA per token: the row of x in shared memory,
-//    a warp per row of G (lanes over k, 16-byte loads), then a thread per group of rows of P, every sum in one fixed
-//    order per output whatever else the step holds;
+//  * token_side_row: all of it in two launches for steps of few tokens.  The first takes a CTA per token and eight
+//    rows of G, a warp per row (lanes over k, 16-byte loads), so that a step of eight tokens still spreads over
+//    dozens of SMs; the second a CTA per token, a thread per row of P, then the norm.  Every sum has one fixed order per
+//    output whatever else the step holds;
 //  * add_row_vector: resid <- resid + dscale * delta + vec.
 //
 // The sums, the activation and the norm are float; G, P and the table are float or bfloat16.
@@ -55,64 +56,90 @@ __global__ void side_gate_mul_kernel(const float* __restrict__ z, const int* __r
     }
 }
 
-// A CTA per token.  Shared memory: the row of x (H floats), g (dim floats), the reduction's scratch.
-template <typename TD, typename T, typename TW>
+// First launch of the one-step form: a CTA per token and group of eight gate outputs, a warp per output.  Every CTA
+// forms the token's row of x in shared memory (the stream is not written here: the CTAs of a token would race).
+template <typename TD, typename T>
 __global__ void __launch_bounds__(256)
-token_side_row_kernel(const TD* __restrict__ delta, float* __restrict__ resid, float dscale,
-                      const int* __restrict__ tokens, const T* __restrict__ table, int ld_table, int col0, int V,
-                      const T* __restrict__ G, const T* __restrict__ P, const TW* __restrict__ w, float eps,
-                      float* __restrict__ out, int H, int dim, int* status) {
-    extern __shared__ __align__(16) float sm[];
-    float* x_s = sm;                               // [H]
-    float* g_s = x_s + ((H + 3) & ~3);             // [dim]
-    float* red = g_s + ((dim + 3) & ~3);           // [33]
-    const size_t t = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float x = resid[t * H + i];
-        if (delta != nullptr) {
-            x = fmaf(dscale, to_float(delta[t * H + i]), x);
-            resid[t * H + i] = x;
-        }
-        x_s[i] = to_float(from_float<T>(x));       // the product's operand in the model's dtype, as the plain path rounds it
-    }
-    __syncthreads();
-    const int id = tokens[t];
-    const bool ok = id >= 0 && id < V;
-    if (!ok && threadIdx.x == 0) set_status(status, STATUS_BAD_TOKEN);
+token_side_gate_kernel(const TD* __restrict__ delta, const float* __restrict__ resid, float dscale,
+                       const int* __restrict__ tokens, const T* __restrict__ table, int ld_table, int col0, int V,
+                       const T* __restrict__ G, float* __restrict__ g_out, int H, int dim, int* status) {
+    extern __shared__ __align__(16) float x_s[];   // [H]
+    const size_t t = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int o = blockIdx.x * 8 + warp;
     constexpr int VEC = 16 / sizeof(T);
     const bool vec = H % VEC == 0 && (uintptr_t)G % 16 == 0;
-    for (int o = warp; o < dim; o += n_warps) {
-        const T* gr = G + (size_t)o * H;
-        float acc = 0.f;
-        if (vec) {
-            for (int c = lane; c < H / VEC; c += 32) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(gr + c * VEC);
-                const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), x_s[c * VEC + j], acc);
-            }
-        } else {
-            for (int k = lane; k < H; k += 32) acc = fmaf(to_float(gr[k]), x_s[k], acc);
-        }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float e = ok ? to_float(table[(size_t)id * ld_table + col0 + o]) : 0.f;
-            g_s[o] = to_float(from_float<T>(gelu_tanh_f(acc) * e));
-        }
+    // this warp's first weights are on their way before the row is there
+    uint4 first = make_uint4(0, 0, 0, 0);
+    if (vec && o < dim && lane < H / VEC) first = *reinterpret_cast<const uint4*>(G + (size_t)o * H + lane * VEC);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = resid[t * H + i];
+        if (delta != nullptr) x = fmaf(dscale, to_float(delta[t * H + i]), x);
+        x_s[i] = to_float(from_float<T>(x));       // the product's operand in the model's dtype, as the other path rounds it
     }
     __syncthreads();
+    if (o >= dim) return;
+    const int id = tokens[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && lane == 0 && blockIdx.x == 0) set_status(status, STATUS_BAD_TOKEN);
+    const T* gr = G + (size_t)o * H;
+    float acc = 0.f;
+    if (vec) {
+        for (int c = lane; c < H / VEC; c += 32) {
+            const uint4 raw = c == lane ? first : *reinterpret_cast<const uint4*>(gr + c * VEC);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), x_s[c * VEC + j], acc);
+        }
+    } else {
+        for (int k = lane; k < H; k += 32) acc = fmaf(to_float(gr[k]), x_s[k], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        const float e = ok ? to_float(table[(size_t)id * ld_table + col0 + o]) : 0.f;
+        g_out[t * dim + o] = to_float(from_float<T>(gelu_tanh_f(acc) * e));
+    }
+}
+
+// Second launch: a CTA per token.  It writes the completed stream back, multiplies the token's gate values by P (a
+// thread per row of P, 16-byte loads where the rows allow them), norms the result and writes the contribution.
+template <typename TD, typename T, typename TW>
+__global__ void __launch_bounds__(256)
+token_side_proj_kernel(const TD* __restrict__ delta, float* __restrict__ resid, float dscale,
+                       const float* __restrict__ g_in, const T* __restrict__ P, const TW* __restrict__ w, float eps,
+                       float* __restrict__ out, int H, int dim) {
+    extern __shared__ __align__(16) float sm[];
+    float* y_s = sm;                               // [H]
+    float* g_s = y_s + ((H + 3) & ~3);             // [dim]
+    float* red = g_s + ((dim + 3) & ~3);           // [33]
+    const size_t t = blockIdx.x;
+    for (int j = threadIdx.x; j < dim; j += blockDim.x) g_s[j] = g_in[t * dim + j];
+    if (delta != nullptr)
+        for (int i = threadIdx.x; i < H; i += blockDim.x)
+            resid[t * H + i] = fmaf(dscale, to_float(delta[t * H + i]), resid[t * H + i]);
+    __syncthreads();
+    constexpr int VEC = 16 / sizeof(T);
+    const bool vec = dim % VEC == 0 && (uintptr_t)P % 16 == 0;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const T* pr = P + (size_t)i * dim;
         float acc = 0.f;
-        for (int j = 0; j < dim; ++j) acc = fmaf(to_float(pr[j]), g_s[j], acc);
-        x_s[i] = acc;                              // x is no longer needed: the row of y takes its place
+        if (vec) {
+            for (int c = 0; c < dim / VEC; ++c) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(pr + c * VEC);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), g_s[c * VEC + j], acc);
+            }
+        } else {
+            for (int j = 0; j < dim; ++j) acc = fmaf(to_float(pr[j]), g_s[j], acc);
+        }
+        y_s[i] = acc;
         ss += acc * acc;
     }
     const float total = block_sum(ss, red);
     const float rstd = rsqrtf(total / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[t * H + i] = x_s[i] * rstd * to_float(w[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[t * H + i] = y_s[i] * rstd * to_float(w[i]);
 }
 
 template <typename TD>
@@ -163,21 +190,28 @@ extern "C" int fd_side_gate_mul(const float* z, const int* tokens, const void* t
                   (const bf16*)table, ld_table, col0, V, (bf16*)g, dim, total, status);
 }
 
-// The whole contribution in one launch; out [T, H] float.  G [dim, H], P [H, dim] and the table of `dtype`; w [H] of
-// w_dtype.  Returns -2 for sizes whose rows do not fit the shared memory (the caller takes the path of separate kernels).
+// The whole contribution in two launches for steps of few tokens; out [T, H] float, g [T, dim] float scratch.  G [dim, H],
+// P [H, dim] and the table of `dtype`; w [H] of w_dtype.  Returns -2 for sizes whose rows do not fit the shared memory
+// (the caller takes the path of separate kernels).
 extern "C" int fd_token_side_row(const void* delta, int delta_dtype, float* resid, float dscale, const int* tokens,
                                  const void* table, int ld_table, int col0, int V, const void* G, const void* P,
-                                 const void* w, int w_dtype, float eps, float* out, int dtype, int T, int H, int dim,
-                                 int* status, cudaStream_t stream) {
+                                 const void* w, int w_dtype, float eps, float* g, float* out, int dtype, int T, int H,
+                                 int dim, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
-    FD_REQUIRE(col0 >= 0 && col0 + dim <= ld_table && dim > 0 && H > 0, -2, "token_side_row: bad sizes");
-    const size_t smem = (((H + 3) & ~3) + ((dim + 3) & ~3) + 40) * sizeof(float);
-    FD_REQUIRE(smem <= 48 * 1024, -2, "token_side_row: a row of %d and %d gate values need %zu bytes of shared memory", H, dim, smem);
-    const dim3 grid(T), block(256), one(1, 1, 1);
+    FD_REQUIRE(col0 >= 0 && col0 + dim <= ld_table && dim > 0 && H > 0 && T <= 65535, -2, "token_side_row: bad sizes");
+    const size_t smem1 = (size_t)((H + 3) & ~3) * sizeof(float);
+    const size_t smem2 = (((H + 3) & ~3) + ((dim + 3) & ~3) + 40) * sizeof(float);
+    FD_REQUIRE(smem2 <= 48 * 1024, -2, "token_side_row: a row of %d and %d gate values need %zu bytes of shared memory", H, dim, smem2);
+    const dim3 grid1((dim + 7) / 8, T), grid2(T), block(256), one(1, 1, 1);
 #define FD_TSR(TD_, T_, TW_)                                                                                          \
-    return launch("token_side_row", token_side_row_kernel<TD_, T_, TW_>, grid, block, smem, stream, one,              \
-                  (const TD_*)delta, resid, dscale, tokens, (const T_*)table, ld_table, col0, V, (const T_*)G,        \
-                  (const T_*)P, (const TW_*)w, eps, out, H, dim, status)
+    do {                                                                                                              \
+        int rc = launch("token_side_gate", token_side_gate_kernel<TD_, T_>, grid1, block, smem1, stream, one,         \
+                        (const TD_*)delta, (const float*)resid, dscale, tokens, (const T_*)table, ld_table, col0, V,  \
+                        (const T_*)G, g, H, dim, status);                                                             \
+        if (rc != 0) return rc;                                                                                       \
+        return launch("token_side_proj", token_side_proj_kernel<TD_, T_, TW_>, grid2, block, smem2, stream, one,      \
+                      (const TD_*)delta, resid, dscale, (const float*)g, (const T_*)P, (const TW_*)w, eps, out, H, dim); \
+    } while (0)
     if (dtype == 0) {
         FD_REQUIRE(w_dtype == 0, -2, "token_side_row: the float path takes float weights");
         if (delta_dtype == 0) FD_TSR(float, float, float);

@@ -97,7 +97,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P, P],
         "fd_conv_rope_append": [P, I, I, P, P, P, P, P, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P, P, F, I, I, P],
-        "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, I, P],
+        "fd_attention_ext": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, I, P, P, F, I, P, I, I, I, P, P],
         "fd_attn_head_mix": [P, P, P, I, I, I, I, I, I, F, P],
         "fd_add_dyn_tanh": [P, I, P, I, P, P, F, P, I, P, I, I, P],
         "fd_quad_exp_act": [P, P, I, P, LL, P],
@@ -122,7 +122,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_moe_gemm": [P, P, P, I, I, P, P, P, I, I, I, I, I, F, I, P],
         "fd_add_cast": [P, I, P, P, I, I, I, F, P],
         "fd_side_gate_mul": [P, P, P, I, I, I, P, I, I, I, P, P],
-        "fd_token_side_row": [P, I, P, F, P, P, I, I, I, P, P, P, I, F, P, I, I, I, I, P, P],
+        "fd_token_side_row": [P, I, P, F, P, P, I, I, I, P, P, P, I, F, P, P, I, I, I, I, P, P],
         "fd_add_row_vector": [P, I, P, P, I, I, F, P],
         "fd_moe_combine": [P, P, P, P, P, P, P, I, I, I, I, I, P],
         "fd_moe_gather": [P, P, P, P, I, I, I, I, P],
@@ -702,7 +702,8 @@ def attention_ext(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, o
                   softcap: float = 0.0, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
                   all_value_heads: bool = False, tensor_cores: bool = True) -> None:
     """Attention with more options, on the CUDA cores; prompt steps in bfloat16 whose key and value heads both have 64
-    or 128 dimensions run on the tensor cores unless ``tensor_cores`` is False.  ``softcap`` > 0: the scaled scores
+    or 128 dimensions run on the tensor cores unless ``tensor_cores`` is False, and so do decode steps in bfloat16 whose
+    only option is ``sink`` (the split-keys decode kernel, at the sizes it takes).  ``softcap`` > 0: the scaled scores
     become softcap * tanh(score / softcap).  ``keep_first``: with a window, keys at positions below it stay
     visible.  ``sink`` [n_q] float32: exp(sink[h]) is one more term of head h's softmax denominator; it has
     no key and no value.  ``all_value_heads``: every query head's weights are applied to each of the ``n_kv``
@@ -719,12 +720,17 @@ def attention_ext(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, o
     if n_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
         assert scratch.numel() >= attention_scratch_floats(T, n_q * v_rep, v_dim, n_splits)
+    # a bfloat16 decode step whose only option is the keyless term may run on the tensor-core decode kernel, which
+    # merges its own splits when it is given counters
+    fused = (n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16 and tensor_cores and sink is not None
+             and not softcap and not (keep_first and window) and not all_value_heads and out.dtype == q.dtype)
     _check(lib().fd_attention_ext(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype), _ptr(block_table), block_table.shape[1],
         num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len),
         n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), int(v_dim), int(chunk), n_splits,
         split_len, _ptr(scratch), _ptr(status), float(softcap), int(keep_first), _ptr(sink), v_rep,
-        int(out.dtype == torch.float32 and q.dtype != torch.float32 or all_value_heads), int(tensor_cores), _stream()))
+        int(out.dtype == torch.float32 and q.dtype != torch.float32 or all_value_heads), int(tensor_cores),
+        _ptr(_counters(q.device, n_rows * n_q)) if fused else None, _stream()))
 
 
 def _col_ptr(t: torch.Tensor, first_col: int) -> int:
@@ -947,17 +953,22 @@ TOKEN_SIDE_ROW_MAX_FLOATS = 12000 - 48      # floats of shared memory the one-la
 
 def token_side_row(delta: Optional[torch.Tensor], resid: torch.Tensor, delta_scale: float, tokens: torch.Tensor,
                    table: torch.Tensor, first_col: int, gate_w: torch.Tensor, proj_w: torch.Tensor,
-                   norm_w: torch.Tensor, eps: float, out: torch.Tensor, status: torch.Tensor) -> None:
-    """In one launch, a CTA per token: resid += delta_scale * delta; g = gelu_tanh(gate_w x) * table[token, first_col ...];
-    y = proj_w g; out = y / sqrt(mean(y^2) + eps) * norm_w (float32 [T, H]).  gate_w [dim, H], proj_w [H, dim]."""
+                   norm_w: torch.Tensor, eps: float, out: torch.Tensor, status: torch.Tensor,
+                   scratch: Optional[torch.Tensor] = None) -> None:
+    """In two launches made for steps of few tokens: resid += delta_scale * delta; g = gelu_tanh(gate_w x) *
+    table[token, first_col ...]; y = proj_w g; out = y / sqrt(mean(y^2) + eps) * norm_w (float32 [T, H]).  gate_w
+    [dim, H], proj_w [H, dim]; ``scratch`` float32 [T, dim] holds g between the launches."""
     T, H = resid.shape
     dim = gate_w.shape[0]
+    if scratch is None:
+        scratch = torch.empty(T, dim, dtype=torch.float32, device=resid.device)
+    assert scratch.dtype == torch.float32 and scratch.numel() >= T * dim
     assert resid.dtype == out.dtype == torch.float32 and out.shape == (T, H) and gate_w.shape == (dim, H)
     assert proj_w.shape == (H, dim) and gate_w.dtype == proj_w.dtype == table.dtype and norm_w.numel() == H
     _check(lib().fd_token_side_row(_ptr(delta), _dt(delta.dtype) if delta is not None else 0, _ptr(resid),
                                    float(delta_scale), _ptr(tokens), _ptr(table), table.shape[1], first_col, table.shape[0],
-                                   _ptr(gate_w), _ptr(proj_w), _ptr(norm_w), _dt(norm_w.dtype), float(eps), _ptr(out),
-                                   _dt(gate_w.dtype), T, H, dim, _ptr(status), _stream()))
+                                   _ptr(gate_w), _ptr(proj_w), _ptr(norm_w), _dt(norm_w.dtype), float(eps), _ptr(scratch),
+                                   _ptr(out), _dt(gate_w.dtype), T, H, dim, _ptr(status), _stream()))
 
 
 def add_row_vector(delta: Optional[torch.Tensor], resid: torch.Tensor, vec: torch.Tensor, delta_scale: float = 1.0) -> None:

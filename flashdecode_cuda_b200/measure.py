@@ -22,7 +22,7 @@ LAUNCHERS = ["embed", "add_rmsnorm", "silu_mul", "rope_append", "gemv_qkv_rope",
              "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine",
              "moe_gather", "gemm_tc_grouped", "glu_mul", "softcap", "lanes_norm", "lanes_fill", "norm_append", "head_gemm",
              "attention_ext", "attn_head_mix", "add_dyn_tanh", "quad_exp_act", "scale_", "axpy_f32", "linear_scan",
-             "head_norm_gate"]
+             "head_norm_gate", "add_cast", "side_gate_mul", "token_side_row", "add_row_vector"]
 
 
 class PartTimer:
@@ -77,6 +77,8 @@ class PartTimer:
                 self._wrap_part(b.mixer, "mixer")
             if getattr(b, "feed_forward", None) is not None:
                 self._wrap_part(b.feed_forward, "feed_forward")
+            if getattr(b, "side", None) is not None:
+                self._wrap_part(b.side, "side_input")
         return self
 
     def __exit__(self, *exc) -> None:
@@ -156,6 +158,14 @@ def part_work(part, ctx_lens: Sequence[int], q_lens: Sequence[int], real_choice_
         flops, byt = _recurrence_inner(part, q_lens)
         nv = part.n_heads * part.dv
         return float(flops + 2 * T * H * part.w_in.shape[0] + 2 * T * nv * H), float(part.weight_bytes() + byt + act)
+    if name == "ChannelDecayAttention":
+        flops, byt = _recurrence_inner(part, q_lens)
+        nk, nv = part.n_heads * part.d, part.n_heads * part.dv
+        products = 2 * T * (H * part.w_in.shape[0] + H * part.rank + part.rank * nk + nv * H)
+        return float(flops + products), float(part.weight_bytes() + byt + act)
+    if name == "GatedTokenRows":
+        # the stream read and written in float32, the contribution written in float32, both small matrices
+        return float(2 * T * 2 * H * part.dim), float(part.weight_bytes() + 3 * T * H * 4 + T * part.dim * el)
     if name == "ParallelMixers":
         # the branches' inner work, and their input and output products once each over the stacked matrices
         flops, byt = 0.0, 0.0

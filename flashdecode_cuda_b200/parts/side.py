@@ -12,8 +12,8 @@ from ..weights.spec import TensorSpec
 from .base import Part, Runtime
 from .linear import matmul
 
-# Up to this many tokens the whole contribution is one launch, a CTA per token (each reads both small matrices);
-# above it the two products go through the matrix-product kernels.
+# Up to this many tokens the whole contribution is two launches whose CTAs each read their share of the small matrices
+# once per token; above it the two products go through the matrix-product kernels.
 SIDE_FUSED_MAX_TOKENS = 64
 
 
@@ -88,7 +88,7 @@ class GatedTokenRows(SideInput):
         if (rt.dtype == torch.bfloat16 and T <= SIDE_FUSED_MAX_TOKENS
                 and H + self.dim + 8 <= K.TOKEN_SIDE_ROW_MAX_FLOATS):
             K.token_side_row(delta, resid, self.delta_scale, ctx.tokens, table, self.first_col, self.w_gate, self.w_proj,
-                             self.norm_w, self.eps, out, rt.status)
+                             self.norm_w, self.eps, out, rt.status, scratch=ws.get("side_z", (T, self.dim), torch.float32))
             return out
         x = ws.get("side_x", (T, H), rt.dtype)
         K.add_cast(delta, resid, x, self.delta_scale)

@@ -144,15 +144,23 @@ def random_config(seed: int) -> dict:
 
 
 def decisive_corrections(folder: Path) -> Path:
-    """Rewrite every router's corrections so that they alone decide the choice (steps of 3 between experts, while
-    scores lie in (0, 1)): in bfloat16 a choice between two nearly equal scores falls either way and says nothing
-    about the kernels."""
+    """Rewrite every router's corrections so that they alone decide the choice: steps of 3 between the experts of a
+    group and far larger steps between the groups, while scores lie in (0, 1).  In bfloat16 a choice between two
+    nearly equal scores, or between two groups whose ranks nearly tie, falls either way and says nothing about the
+    kernels."""
     cfg = raw_config(folder)
     W = weights_of(folder)
     for name in [n for n in W if n.endswith(".correction")]:
+        layer = int(name.split(".")[0][1:])
         n = W[name].numel()
-        g = torch.Generator().manual_seed(n + len(name))
-        W[name] = (torch.randperm(n, generator=g).float() * 3.0).to(W[name].dtype)
+        groups = (cfg["layers"][layer]["mlp"]["router"].get("groups") or {"count": 1})["count"]
+        per = n // groups
+        g = torch.Generator().manual_seed(n + 7 * layer)
+        order = torch.randperm(groups, generator=g)
+        corr = torch.zeros(n)
+        for k in range(groups):
+            corr[k * per:(k + 1) * per] = 3.0 * (order[k] * 2 * per + torch.randperm(per, generator=g)).float()
+        W[name] = corr.to(W[name].dtype)
     write_model_folder(folder, cfg, W)
     return folder
 
@@ -181,9 +189,9 @@ SINGLE_PRECISION_DISTANCE = 5e-7
 # order of summation differs from the float64 ground truth.  bfloat16: products and activations are rounded to 8 bits
 # of mantissa layer after layer, and this design renormalises vectors that partly cancel in every layer (each q and k
 # head after its convolution, the token's own contribution over its root mean square): the library's bfloat16 path
-# measures 0.02 to 0.08 on these configurations where the plain model run wholly in bfloat16 lies at 0.3 to 0.5.  What
+# measures 0.01 to 0.07 on these configurations where the plain model run wholly in bfloat16 lies at 0.05 to 0.5.  What
 # a wrong mask, state or page does is told apart by the float32 runs and by the kernel tests with keys that stand out.
-MODEL_TOL = {"float32": 1e-4, "bfloat16": 1e-1}
+MODEL_TOL = {"float32": 1e-4, "bfloat16": 8e-2}
 
 
 class Truth:

@@ -362,9 +362,9 @@ def test_sigmoid_scores_and_the_choice_among_the_best_groups(dtype, case, T):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,H,dim", [(1, 64, 16), (5, 100, 4), (64, 256, 20), (65, 256, 20), (300, 1032, 32), (7, 72, 1)])
-def test_token_side_input_in_one_launch_and_as_separate_kernels(dtype, T, H, dim):
+def test_token_side_input_for_few_tokens_and_as_separate_kernels(dtype, T, H, dim):
     """out = unit_rms(P (gelu(G x) * e)) * w with x = resid + c * delta completed on the way, against the plain
-    function: the one-launch form (bfloat16, few tokens) and the form whose products are matrix products."""
+    function: the form for steps of few tokens (bfloat16) and the form whose products are matrix products."""
     torch.manual_seed(T + H + dim)
     dt = TD[dtype]
     V, layers, layer, c = 37, 3, 1, 0.3
@@ -378,11 +378,11 @@ def test_token_side_input_in_one_launch_and_as_separate_kernels(dtype, T, H, dim
     x_in = x.to(dt).double() if dtype == "bfloat16" else x          # the product's operand is the stream in the model's dtype
     want = P.token_side(x_in, tokens, Wd, layer, dim, 1e-5)
     status = new_status()
-    forms = ["separate"] + (["one launch"] if T <= 64 and dtype == "bfloat16" else [])
+    forms = ["separate"] + (["few launches"] if T <= 64 and dtype == "bfloat16" else [])
     from flashdecode_cuda_b200.parts.linear import matmul
     for form in forms:
         r, out = resid.to(DEV), torch.full((T, H), float("nan"), device=DEV)
-        if form == "one launch":
+        if form == "few launches":
             K.token_side_row(delta.to(DEV), r, c, i32(tokens.tolist()), table.to(DEV), layer * dim, G.to(DEV), Pm.to(DEV),
                              w.to(DEV), 1e-5, out, status)
         else:
