@@ -185,6 +185,9 @@ def weights_of(folder: Path) -> Dict[str, torch.Tensor]:
 _ORACLE: dict = {}
 
 SINGLE_PRECISION_DISTANCE = 5e-7
+# |cos| of the angle between the first token's q and k of a linear-attention head below which bfloat16 may flip the
+# sign of that head's first output (see ``Truth``); about one sequence in five has such a head among half a dozen
+FIRST_TOKEN_MARGIN = 0.01
 # Whole models, relative to the largest logit of the sequence, where nothing amplifies rounding.  float32: only the
 # order of summation differs from the float64 ground truth.  bfloat16: products and activations are rounded to 8 bits
 # of mantissa layer after layer, and this design renormalises vectors that partly cancel in every layer (each q and k
@@ -201,14 +204,26 @@ class Truth:
     implementation; such a position is allowed that much more."""
 
     def __init__(self, cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int]):
-        self.logits = P.forward(cfg, W, tokens)
+        captures: list = []
+        self.logits = P.forward(cfg, W, tokens, captures=captures)
         self.scale = max(float(self.logits.abs().max()), 1e-6)
+        # The first token's output of a linear-attention head is (q . k) v, and the norm that follows leaves v / rms(v)
+        # times the SIGN of q . k: where q and k are nearly at right angles, rounding to 8 bits decides that sign, and
+        # the state carries the difference on.  Such a sequence says nothing about the bfloat16 path.
+        self.first_margin = 1.0
+        for _, kind, cap in captures:
+            if kind == "gla":
+                q0, k0 = cap["q"][0], cap["k"][0]
+                cos = (q0 * k0).sum(-1).abs() / (q0.norm(dim=-1) * k0.norm(dim=-1) + 1e-30)
+                self.first_margin = min(self.first_margin, float(cos.min()))
         single = P.forward(cfg, W, tokens, dtype=torch.float32).double()
         self.single = (single - self.logits).abs().amax(-1) / self.scale               # [len]
 
     def allowed(self, dtype: str) -> torch.Tensor:
         if dtype == "float32":
             return torch.clamp(6 * self.single, min=MODEL_TOL[dtype])
+        if self.first_margin < FIRST_TOKEN_MARGIN:
+            return torch.full_like(self.single, float("inf"))
         return MODEL_TOL[dtype] * torch.clamp(self.single / SINGLE_PRECISION_DISTANCE, min=1.0)
 
     def excess(self, got: torch.Tensor, rows, dtype: str) -> float:

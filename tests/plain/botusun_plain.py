@@ -233,8 +233,10 @@ def layer_runs(cfg: dict) -> List[tuple]:
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, return_layers: bool = False):
-    """Logits [S, vocab] of one whole sequence (and, on request, the stream after every layer run)."""
+def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, return_layers: bool = False,
+            captures: Optional[list] = None):
+    """Logits [S, vocab] of one whole sequence (and, on request, the stream after every layer run).  ``captures``: a
+    list that receives (layer, type, what the mixer saw) for every layer run."""
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
@@ -246,12 +248,15 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.flo
         if t is not None:
             x = x + W["loop.step"][t]
         h = rms_norm(x, W[f"{p}.norm1"], eps)
+        cap = None if captures is None else {}
         if L["type"] == "gla":
-            x = x + m * gla_mixer(h, W, f"{p}.mix", L["mixer"], eps)
+            x = x + m * gla_mixer(h, W, f"{p}.mix", L["mixer"], eps, cap)
         elif L["type"] == "attention":
-            x = x + m * attention_mixer(h, W, f"{p}.mix", L["mixer"], eps)
+            x = x + m * attention_mixer(h, W, f"{p}.mix", L["mixer"], eps, cap)
         else:
             raise ValueError(L["type"])
+        if captures is not None:
+            captures.append((i, L["type"], cap))
         fc = L.get("mlp")
         if fc:
             h = rms_norm(x, W[f"{p}.norm2"], eps)
