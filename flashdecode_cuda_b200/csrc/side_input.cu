@@ -56,7 +56,7 @@ __global__ void side_gate_mul_kernel(const float* __restrict__ z, const int* __r
     }
 }
 
-// First launch of the one-step form: a CTA per token and group of eight gate outputs, a warp per output.  Every CTA
+// First launch of the form for few tokens: a CTA per token and group of eight gate outputs, a warp per output.  Every CTA
 // forms the token's row of x in shared memory (the stream is not written here: the CTAs of a token would race).
 template <typename TD, typename T>
 __global__ void __launch_bounds__(256)
@@ -85,11 +85,21 @@ token_side_gate_kernel(const TD* __restrict__ delta, const float* __restrict__ r
     const T* gr = G + (size_t)o * H;
     float acc = 0.f;
     if (vec) {
-        for (int c = lane; c < H / VEC; c += 32) {
-            const uint4 raw = c == lane ? first : *reinterpret_cast<const uint4*>(gr + c * VEC);
-            const T* e = reinterpret_cast<const T*>(&raw);
+        for (int c0 = lane; c0 < H / VEC; c0 += 4 * 32) {          // four 16-byte loads of the row in flight together
+            uint4 raw[4];
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), x_s[c * VEC + j], acc);
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * 32;
+                if (c < H / VEC) raw[u] = c == lane ? first : *reinterpret_cast<const uint4*>(gr + c * VEC);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = c0 + u * 32;
+                if (c >= H / VEC) continue;
+                const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), x_s[c * VEC + j], acc);
+            }
         }
     } else {
         for (int k = lane; k < H; k += 32) acc = fmaf(to_float(gr[k]), x_s[k], acc);
@@ -104,7 +114,7 @@ token_side_gate_kernel(const TD* __restrict__ delta, const float* __restrict__ r
 // Second launch: a CTA per token.  It writes the completed stream back, multiplies the token's gate values by P (a
 // thread per row of P, 16-byte loads where the rows allow them), norms the result and writes the contribution.
 template <typename TD, typename T, typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 token_side_proj_kernel(const TD* __restrict__ delta, float* __restrict__ resid, float dscale,
                        const float* __restrict__ g_in, const T* __restrict__ P, const TW* __restrict__ w, float eps,
                        float* __restrict__ out, int H, int dim) {
@@ -113,23 +123,39 @@ token_side_proj_kernel(const TD* __restrict__ delta, float* __restrict__ resid, 
     float* g_s = y_s + ((H + 3) & ~3);             // [dim]
     float* red = g_s + ((dim + 3) & ~3);           // [33]
     const size_t t = blockIdx.x;
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int AHEAD = 4;                       // 16-byte loads of a row in flight together
+    const bool vec = dim % VEC == 0 && (uintptr_t)P % 16 == 0;
+    // the first loads of this thread's first row need nothing but P: they are on their way while g arrives
+    uint4 first[AHEAD];
+    if (vec && threadIdx.x < H) {
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u)
+            if (u < dim / VEC) first[u] = *reinterpret_cast<const uint4*>(P + (size_t)threadIdx.x * dim + u * VEC);
+    }
     for (int j = threadIdx.x; j < dim; j += blockDim.x) g_s[j] = g_in[t * dim + j];
     if (delta != nullptr)
         for (int i = threadIdx.x; i < H; i += blockDim.x)
             resid[t * H + i] = fmaf(dscale, to_float(delta[t * H + i]), resid[t * H + i]);
     __syncthreads();
-    constexpr int VEC = 16 / sizeof(T);
-    const bool vec = dim % VEC == 0 && (uintptr_t)P % 16 == 0;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const T* pr = P + (size_t)i * dim;
         float acc = 0.f;
         if (vec) {
-            for (int c = 0; c < dim / VEC; ++c) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(pr + c * VEC);
-                const T* e = reinterpret_cast<const T*>(&raw);
+            for (int c0 = 0; c0 < dim / VEC; c0 += AHEAD) {
+                uint4 raw[AHEAD];
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), g_s[c * VEC + j], acc);
+                for (int u = 0; u < AHEAD; ++u)
+                    if (c0 + u < dim / VEC)
+                        raw[u] = (c0 == 0 && i == threadIdx.x) ? first[u] : *reinterpret_cast<const uint4*>(pr + (c0 + u) * VEC);
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) {
+                    if (c0 + u >= dim / VEC) continue;
+                    const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) acc = fmaf(to_float(e[j]), g_s[(c0 + u) * VEC + j], acc);
+                }
             }
         } else {
             for (int j = 0; j < dim; ++j) acc = fmaf(to_float(pr[j]), g_s[j], acc);
@@ -203,13 +229,14 @@ extern "C" int fd_token_side_row(const void* delta, int delta_dtype, float* resi
     const size_t smem2 = (((H + 3) & ~3) + ((dim + 3) & ~3) + 40) * sizeof(float);
     FD_REQUIRE(smem2 <= 48 * 1024, -2, "token_side_row: a row of %d and %d gate values need %zu bytes of shared memory", H, dim, smem2);
     const dim3 grid1((dim + 7) / 8, T), grid2(T), block(256), one(1, 1, 1);
+    const dim3 block2(H >= 1024 ? 1024 : (H >= 512 ? 512 : 256));
 #define FD_TSR(TD_, T_, TW_)                                                                                          \
     do {                                                                                                              \
         int rc = launch("token_side_gate", token_side_gate_kernel<TD_, T_>, grid1, block, smem1, stream, one,         \
                         (const TD_*)delta, (const float*)resid, dscale, tokens, (const T_*)table, ld_table, col0, V,  \
                         (const T_*)G, g, H, dim, status);                                                             \
         if (rc != 0) return rc;                                                                                       \
-        return launch("token_side_proj", token_side_proj_kernel<TD_, T_, TW_>, grid2, block, smem2, stream, one,      \
+        return launch("token_side_proj", token_side_proj_kernel<TD_, T_, TW_>, grid2, block2, smem2, stream, one,      \
                       (const TD_*)delta, resid, dscale, (const float*)g, (const T_*)P, (const TW_*)w, eps, out, H, dim); \
     } while (0)
     if (dtype == 0) {
