@@ -97,7 +97,7 @@ def random_config(seed: int) -> dict:
     frequencies, windows from one position to longer than any test sequence, dense and routed feed-forwards and none,
     loops over any span (also all layers, also once), with and without the side input."""
     rng = random.Random(seed)
-    width = rng.choice([48, 72, 96, 128, 200, 256])
+    width = rng.choice([36, 48, 72, 96, 100, 128, 200, 256])
 
     def rotation(dim):
         if rng.random() < 0.15:

@@ -556,6 +556,28 @@ def test_unequal_batch_equals_each_request_alone_and_slots_are_used_again(engine
     eng.model.check_status()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_two_dozen_requests_decoded_together(engines, folders, dtype):
+    """More rows than the register-fed products take: the step's products, the routing and the side input run in their
+    forms for 17 to 128 rows; every request's logits equal those of the request alone."""
+    name = "A"
+    eng, folder = engines[(name, dtype)], folders[(name, dtype)]
+    reqs = prompts_for(_vocab(name), [3 + (7 * i) % 45 for i in range(24)], seed=60)
+    heads = [max(1, len(p) - 4) for p in reqs]
+    cache = eng.model.new_cache(max_tokens=64 * 24, block_size=16, max_slots=24)
+    slots = [cache.admit() for _ in reqs]
+    got = eng.model.step(cache, slots, [p[:h] for p, h in zip(reqs, heads)], "last")
+    for i, (p, h) in enumerate(zip(reqs, heads)):
+        assert truth(folder, p).excess(got[i], [h - 1], dtype) < 1, f"request {i}"
+    for step in range(3):
+        live = [i for i in range(24) if heads[i] + step < len(reqs[i])]
+        got = eng.model.step(cache, [slots[i] for i in live], [[reqs[i][heads[i] + step]] for i in live], "last")
+        for j, i in enumerate(live):
+            assert truth(folder, reqs[i]).excess(got[j], [heads[i] + step], dtype) < 1, f"request {i}, decoded token {step}"
+    eng.model.check_status()
+    cache.check_invariants()
+
+
 def test_batch_neighbours_change_no_bit_in_float32(engines):
     for name in NAMES:
         eng = engines[(name, "float32")]
