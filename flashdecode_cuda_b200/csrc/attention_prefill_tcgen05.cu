@@ -485,6 +485,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (n_mine - 1) & 1, abort_flag, p.status, wait_ns));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // a keyless term exp(sink[h]) joins the denominator: relative to the running maximum, like every other term
+        const float sink_log2 = p.sink != nullptr ? p.sink[h] * 1.4426950408889634f : 0.f;
+        if (!SPLIT && p.sink != nullptr && l_run > 0.f) l_run += ta_ex2(sink_log2 - m_run * scale_log2);
         float w_own = l_run > 0.f ? 1.f / l_run : 0.f;          // what this thread's O is multiplied by
         float w_other = 0.f;                                    // SPLIT: and the other group's
         const float* o_other = nullptr;
@@ -520,7 +523,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const float m = fmaxf(m0, m1);
                 const float a0 = m0 == -INFINITY ? 0.f : ta_ex2(m0 - m);
                 const float a1 = m1 == -INFINITY ? 0.f : ta_ex2(m1 - m);
-                const float l = l_run * a0 + l1 * a1;
+                float l = l_run * a0 + l1 * a1;
+                if (p.sink != nullptr && l > 0.f) l += ta_ex2(sink_log2 - m);
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 w_own = a0 * inv;
                 w_other = a1 * inv;

@@ -535,7 +535,11 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
         rc = use_mma == 2 ? 1 : launch_attn_prefill_tcgen05(p, n_rows, T, max_q_len, stream);
         if (rc == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
     }
-    if (ext && ext_mma && dtype == 1 && max_q_len > 1) rc = launch_attn_prefill_mma_ext(p, n_rows, max_q_len, stream);
+    if (ext && ext_mma && dtype == 1 && max_q_len > 1) {
+        // of the options the tcgen05 prompt kernel has the keyless term too (head size 128)
+        if (sink_only && dv == d) rc = launch_attn_prefill_tcgen05(p, n_rows, T, max_q_len, stream);
+        if (rc == 1) rc = launch_attn_prefill_mma_ext(p, n_rows, max_q_len, stream);
+    }
     if (rc == 1)
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);
