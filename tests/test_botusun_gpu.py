@@ -651,10 +651,11 @@ def test_configurations_drawn_at_random_in_bfloat16(tmp_path, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_prompts_at_sizes_of_the_tensor_core_kernels(tmp_path, dtype):
-    """Heads of 64 and 128, experts wide enough for the grouped tensor-core products, prompts of several hundred tokens:
+    """Heads of 64 and 128, a width and experts wide enough for the grouped tcgen05 products with the gate in their
+    epilogue, prompts of several hundred tokens:
     many segments of the recurrence, windows that leave most key tiles unvisited, a key far back under a long window;
     every position of each prompt alone, then the two together and decoded on."""
-    cfg = BH.model(333, 128, 1e-5, [
+    cfg = BH.model(333, 256, 1e-5, [
         BH.gla(2, 64, 64, 16.0, 16, BH.dense(96)),
         BH.attention(4, 2, 64, 3, 0.125, window=150, rotation=BH.rot(32, 10000.0, (4.0, 1.0, 4.0, 64)),
                      mlp=BH.moe(8, 2, 128, groups=(4, 2), scale=1.5)),
