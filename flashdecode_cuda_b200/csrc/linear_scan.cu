@@ -30,6 +30,8 @@
 //  3. every segment walks its tokens again from its S_s and writes the outputs; the last one writes the state back.
 // The recurrence itself is unchanged, so nothing is divided by a product of gates that could vanish.
 //
+//  * low_rank_expand: a narrow vector per token times a matrix [N, R] plus a bias, as floats (the pre-activation of a
+//    decay that comes through a narrow projection);
 //  * head_norm_gate: y = o / sqrt(mean(o^2) + eps) per token and head (over dv), times an optional weight [dv], times
 //    an optional silu(gate) read from a column range of a packed projection, times a constant; written with a row
 //    stride and a column offset of its own so that several mixers can fill one buffer.
@@ -385,6 +387,68 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
     }
 }
 
+
+// out[t, c] = bias[c] + sum_r w[c, r] * x[t, x_col + r]: a narrow vector per token (R <= EXPAND_MAX_R columns of a wider
+// matrix) expanded to N channels, float sums in the order r = 0, 1, ... from the bias on, whatever else the step holds.
+// A CTA of two warps takes 64 channels and up to EXPAND_TOK tokens, so that a decode step still spreads over dozens of
+// SMs: the tokens' vectors wait in shared memory as floats (every thread reads the same one: a broadcast), and a thread
+// streams its own row of w with 16-byte loads, several in flight.
+constexpr int EXPAND_MAX_R = 64;
+constexpr int EXPAND_TOK = 8;
+constexpr int EXPAND_CH = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(EXPAND_CH)
+low_rank_expand_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ w, const float* __restrict__ bias,
+                       float* __restrict__ out, int n_tok, int N, int R) {
+    __shared__ __align__(16) float x_s[EXPAND_TOK * EXPAND_MAX_R];
+    const int c = blockIdx.x * EXPAND_CH + threadIdx.x, t0 = blockIdx.y * EXPAND_TOK;
+    const int nt = min(EXPAND_TOK, n_tok - t0);
+    for (int e = threadIdx.x; e < EXPAND_TOK * R; e += EXPAND_CH) {
+        const int tt = e / R, r = e - tt * R;
+        x_s[e] = tt < nt ? to_float(x[(size_t)(t0 + tt) * ldx + r]) : 0.f;
+    }
+    __syncthreads();
+    if (c >= N) return;
+    const float b = bias != nullptr ? bias[c] : 0.f;
+    const T* wr = w + (size_t)c * R;
+    float acc[EXPAND_TOK];
+#pragma unroll
+    for (int tt = 0; tt < EXPAND_TOK; ++tt) acc[tt] = b;
+    constexpr int VEC = 16 / sizeof(T);
+    if (R % VEC == 0 && (uintptr_t)w % 16 == 0) {
+#pragma unroll 4
+        for (int r0 = 0; r0 < R; r0 += VEC) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(wr + r0);
+            const T* e = reinterpret_cast<const T*>(&raw);
+            float wv[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) wv[j] = to_float(e[j]);
+#pragma unroll
+            for (int tt = 0; tt < EXPAND_TOK; ++tt) {
+                // four values of the token's vector per shared-memory load; the sum still runs over r in order
+#pragma unroll
+                for (int j4 = 0; j4 < VEC; j4 += 4) {
+                    const float4 xv = *reinterpret_cast<const float4*>(x_s + tt * R + r0 + j4);
+                    acc[tt] = fmaf(wv[j4], xv.x, acc[tt]);
+                    acc[tt] = fmaf(wv[j4 + 1], xv.y, acc[tt]);
+                    acc[tt] = fmaf(wv[j4 + 2], xv.z, acc[tt]);
+                    acc[tt] = fmaf(wv[j4 + 3], xv.w, acc[tt]);
+                }
+            }
+        }
+    } else {
+        for (int r = 0; r < R; ++r) {
+            const float wv = to_float(wr[r]);
+#pragma unroll
+            for (int tt = 0; tt < EXPAND_TOK; ++tt) acc[tt] = fmaf(wv, x_s[tt * R + r], acc[tt]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < EXPAND_TOK; ++tt)
+        if (tt < nt) out[(size_t)(t0 + tt) * N + c] = acc[tt];
+}
+
 }  // namespace fd
 
 using namespace fd;
@@ -508,4 +572,19 @@ extern "C" int fd_head_norm_gate(const float* o, const float* w, const void* gat
                       (const float*)gate, ldg, (float*)out, ld_out, (int)pairs, H, dv, eps, scale);
     return launch("head_norm_gate", head_norm_gate_kernel<bf16>, grid, dim3(128), 0, stream, dim3(1, 1, 1), o, w,
                   (const bf16*)gate, ldg, (bf16*)out, ld_out, (int)pairs, H, dv, eps, scale);
+}
+
+// x: pointer to the first of the R columns of a matrix [T, ldx] of `dtype` (0 float32, 1 bfloat16); w [N, R] of the same
+// type; bias [N] float or null; out [T, N] float.  R at most 64.
+extern "C" int fd_low_rank_expand(const void* x, int ldx, const void* w, const float* bias, float* out, int dtype, int T,
+                                  int N, int R, cudaStream_t stream) {
+    if (T == 0 || N == 0) return 0;
+    FD_REQUIRE(R >= 1 && R <= EXPAND_MAX_R && ldx >= R, -2, "low_rank_expand: %d columns of rows of %d (at most %d)", R, ldx, EXPAND_MAX_R);
+    const dim3 grid((N + EXPAND_CH - 1) / EXPAND_CH, (T + EXPAND_TOK - 1) / EXPAND_TOK);
+    FD_REQUIRE(grid.y <= 65535, -2, "low_rank_expand: %d tokens are too many", T);
+    if (dtype == 0)
+        return launch("low_rank_expand", low_rank_expand_kernel<float>, grid, dim3(EXPAND_CH), 0, stream, dim3(1, 1, 1),
+                      (const float*)x, ldx, (const float*)w, bias, out, T, N, R);
+    return launch("low_rank_expand", low_rank_expand_kernel<bf16>, grid, dim3(EXPAND_CH), 0, stream, dim3(1, 1, 1),
+                  (const bf16*)x, ldx, (const bf16*)w, bias, out, T, N, R);
 }

@@ -105,6 +105,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_axpy_f32": [P, P, I, LL, F, I, P],
         "fd_linear_scan": [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, F, P, P, P, P, I, I, I, I, I, P, I, I, P, LL, P, I, F, F, P],
         "fd_head_norm_gate": [P, P, P, I, P, I, I, I, I, I, F, F, P],
+        "fd_low_rank_expand": [P, I, P, P, P, I, I, I, I, P],
         "fd_conv_state_update": [P, I, I, P, P, P, P, I, I, I, P],
         "fd_gate_mul": [P, P, I, P, I, I, I, P],
         "fd_add_concat": [P, I, P, P, P, I, I, I, P],
@@ -837,6 +838,19 @@ def linear_scan_segment() -> int:
 def linear_scan_scratch_floats(T: int, n_rows: int, n_heads: int, head_dim: int, v_head_dim: int) -> int:
     """float32 elements of scratch memory with which ``linear_scan`` runs a step of T tokens in n_rows sequences in segments."""
     return int(lib().fd_linear_scan_scratch_floats(T, n_rows, n_heads, head_dim, v_head_dim))
+
+
+LOW_RANK_EXPAND_MAX = 64        # widest vector ``low_rank_expand`` takes
+
+
+def low_rank_expand(x: torch.Tensor, first_col: int, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t, c] = bias[c] + sum_r w[c, r] * x[t, first_col + r]; x [T, ld] and w [N, R] in the model's dtype (R at most
+    ``LOW_RANK_EXPAND_MAX``), bias float32 [N] or None, out float32 [T, N].  Float sums in the order r = 0, 1, ..."""
+    T, (N, R) = x.shape[0], w.shape
+    assert x.dtype == w.dtype and out.dtype == torch.float32 and out.shape == (T, N) and first_col + R <= x.shape[1]
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
+    _check(lib().fd_low_rank_expand(_col_ptr(x, first_col), x.shape[1], _ptr(w), _ptr(bias), _ptr(out), _dt(x.dtype),
+                                    T, N, R, _stream()))
 
 
 def head_norm_gate(o: torch.Tensor, out: torch.Tensor, first_col: int, n_heads: int, v_head_dim: int, eps: float,

@@ -22,7 +22,7 @@ LAUNCHERS = ["embed", "add_rmsnorm", "silu_mul", "rope_append", "gemv_qkv_rope",
              "conv_state_update", "gate_mul", "add_concat", "relu2", "moe_route", "moe_align", "moe_gemm", "moe_combine",
              "moe_gather", "gemm_tc_grouped", "glu_mul", "softcap", "lanes_norm", "lanes_fill", "norm_append", "head_gemm",
              "attention_ext", "attn_head_mix", "add_dyn_tanh", "quad_exp_act", "scale_", "axpy_f32", "linear_scan",
-             "head_norm_gate", "add_cast", "side_gate_mul", "token_side_row", "add_row_vector"]
+             "head_norm_gate", "add_cast", "side_gate_mul", "token_side_row", "add_row_vector", "low_rank_expand"]
 
 
 class PartTimer:

@@ -169,8 +169,9 @@ class ChannelDecayAttention(_StateMixer):
         S_t = diag(a_t) S_(t-1) + k_t v_t^T;   o_t = S_t^T q_t
         out = W_o ( concat_h o_t / rms(o_t) * w * silu(W_g h) )                       (w [v_head_dim], shared by heads)
 
-    The state starts at zero and is carried in float32 per cache slot; the decay's pre-activation leaves its product as
-    float32, and the sigmoid, its logarithm, the power, the state, the output and the norm are float32 in both dtypes.
+    The state starts at zero and is carried in float32 per cache slot.  W_a1 of up to 64 rows rides in the packed input
+    product and one kernel expands its output to the channels (``low_rank_expand``); the decay's pre-activation is
+    float32 either way, and the sigmoid, its logarithm, the power, the state, the output and the norm are float32 in both dtypes.
     Tensors ``<prefix>.q`` / ``.k`` / ``.v`` / ``.g`` / ``.o`` / ``.norm`` / ``.a1`` / ``.a2`` / ``.a2.b``.
     ``decay_rank`` (the rows of W_a1) None: the checkpoint's tensors give it."""
 
@@ -198,28 +199,36 @@ class ChannelDecayAttention(_StateMixer):
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
-        self.w_in = torch.cat([tensors.pop(f"{p}.{n}") for n in "qkvg"], dim=0).contiguous()
-        self.b_in = None
         self.w_a1, self.w_a2 = tensors[f"{p}.a1"], tensors[f"{p}.a2"]
         if self.w_a1.shape[0] != self.w_a2.shape[1]:
             raise ValueError(f"{p}: a1 has {self.w_a1.shape[0]} rows and a2 {self.w_a2.shape[1]} columns")
         self.rank = self.w_a1.shape[0]
+        # a narrow projection rides in the packed input product, and one kernel expands it to the channels; a wide one
+        # keeps two products of its own
+        self.packed_decay = self.rank <= K.LOW_RANK_EXPAND_MAX
+        mats = [tensors.pop(f"{p}.{n}") for n in "qkvg"] + ([self.w_a1] if self.packed_decay else [])
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        self.b_in = None
         self.b_a2 = tensors.pop(f"{p}.a2.b").float().contiguous()
         self.norm_w = tensors.pop(f"{p}.norm").float().contiguous()
         self.w_o = tensors[f"{p}.o"]
 
     def weight_bytes(self) -> int:
-        return super().weight_bytes() + (self.w_a1.numel() + self.w_a2.numel()) * self.w_a1.element_size()
+        own = 0 if self.packed_decay else self.w_a1.numel() * self.w_a1.element_size()
+        return super().weight_bytes() + own + self.w_a2.numel() * self.w_a2.element_size()
 
     def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
         T, ws, rt = ctx.T, ctx.ws, self.rt
         nk, nv = self.n_heads * self.d, self.n_heads * self.dv
         proj = ws.get("rec_proj", (T, self.w_in.shape[0]), x.dtype)
         matmul(x, self.w_in, None, proj, status=rt.status)
-        low = ws.get("rec_decay_low", (T, self.rank), x.dtype)
-        matmul(x, self.w_a1, None, low, status=rt.status)
         z = ws.get("rec_decay_z", (T, nk), torch.float32)
-        matmul(low, self.w_a2, self.b_a2, z, status=rt.status)
+        if self.packed_decay:
+            K.low_rank_expand(proj, 2 * nk + 2 * nv, self.w_a2, self.b_a2, z)
+        else:
+            low = ws.get("rec_decay_low", (T, self.rank), x.dtype)
+            matmul(x, self.w_a1, None, low, status=rt.status)
+            matmul(low, self.w_a2, self.b_a2, z, status=rt.status)
         o = ws.get("scan_out", (T, nv), torch.float32)
         K.linear_scan(proj, 0, nk, 2 * nk, lc.states["state"], o, K.SCAN_CHANNEL_DECAY, ctx.row_slot, ctx.row_q_start,
                       ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, self.n_heads, self.d, self.dv, lc.writes, rt.status,
